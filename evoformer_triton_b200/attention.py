@@ -1,0 +1,259 @@
+"""Host side of the Evoformer attention op: the reference's autograd boundary.
+
+``EvoformerAttention`` mirrors dsevoformer-triton/evoformer.py:633-862: same class
+name, same ``apply(Q, K, V, res_mask, pair_bias)`` call on ``[B, N_seq, N_res, H, D]``
+tensors, same reinterpretation of those tensors as ``[B, H, N_seq, N_res, D]``
+(evoformer.py:648-650), same ``(dQ, dK, dV, None, d_pair_bias)`` gradients.  The device
+work is done by libevoattn.so through its C ABI; torch is used for memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.FP16, torch.float32: _lib.FP32}
+
+# Launch counters the benchmark reads (kernels of this library only).
+launches = {"fwd": 0, "bwd": 0}
+last_path = {"fwd": _lib.PATH_NONE, "bwd": _lib.PATH_NONE}
+_force_generic = bool(int(os.environ.get("EVOATTN_FORCE_GENERIC", "0")))
+_status_words = {}
+
+
+def force_generic(on: bool) -> None:
+    """Route every call to the CUDA-core kernels (used by tests to cross-check)."""
+    global _force_generic
+    _force_generic = bool(on)
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    """One int32 per device that kernels set when they give up a bounded wait."""
+    t = _status_words.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[device] = t
+    return t
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if any kernel reported a timed-out wait."""
+    for dev, t in list(_status_words.items()):
+        if device is not None and torch.device(device) != dev:
+            continue
+        v = int(t.item())
+        if v != 0:
+            t.zero_()
+            raise RuntimeError(f"evoattn kernel on {dev} gave up a bounded wait (device status {v})")
+
+
+def _strides4(t: torch.Tensor):
+    st = t.stride()
+    return (C.c_int64 * 4)(st[0], st[1], st[2], st[3])
+
+
+def _require_cuda(t: torch.Tensor):
+    if not t.is_cuda:
+        raise RuntimeError("EvoformerAttention runs on CUDA tensors only; there is no CPU fallback")
+
+
+def _fill_fwd(p: "_lib.FwdParams", q, k, v, o, lse, mask, bias, scale):
+    B, H, S, R, D = q.shape
+    p.dtype = _DTYPES[q.dtype]
+    p.B, p.H, p.S, p.R, p.D = B, H, S, R, D
+    p.scale = float(scale)
+    p.flags = _lib.FLAG_FORCE_GENERIC if _force_generic else 0
+    p.q, p.k, p.v, p.o, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
+    p.q_stride, p.k_stride, p.v_stride, p.o_stride = _strides4(q), _strides4(k), _strides4(v), _strides4(o)
+    if mask is None:
+        p.mask, p.mask_kind = None, _lib.MASK_NONE
+    else:
+        p.mask = mask.data_ptr()
+        if mask.dtype == torch.bool:
+            p.mask_kind = _lib.MASK_BOOL
+        elif mask.dtype == torch.float32:
+            p.mask_kind = _lib.MASK_ADD_F32
+        elif mask.dtype == q.dtype:
+            p.mask_kind = _lib.MASK_ADD_SAME
+        else:
+            raise TypeError(f"res_mask dtype {mask.dtype} not supported (bool, float32 or the q/k/v dtype)")
+        ms = mask.stride()
+        p.mask_stride = (C.c_int64 * 3)(ms[0], ms[1], ms[2])
+    if bias is None:
+        p.bias = None
+    else:
+        p.bias = bias.data_ptr()
+        bs = bias.stride()
+        p.bias_stride = (C.c_int64 * 3)(bs[0], bs[1], bs[2])
+    p.status = _status_word(q.device).data_ptr()
+
+
+def _view_dims(x: torch.Tensor, layout: str) -> torch.Tensor:
+    """[B,S,R,H,D] -> the [B,H,S,R,D] attention view (no copy for contiguous input)."""
+    B, S, R, H, D = x.shape
+    if layout == "reinterpret":
+        return x.reshape(B, H, S, R, D)  # evoformer.py:648-650
+    return x.permute(0, 3, 1, 2, 4)
+
+
+def _unview(x: torch.Tensor, layout: str) -> torch.Tensor:
+    B, H, S, R, D = x.shape
+    if layout == "reinterpret":
+        return x.reshape(B, S, R, H, D)  # evoformer.py:735
+    return x.permute(0, 2, 3, 1, 4)
+
+
+def _prep_operand(x: torch.Tensor) -> torch.Tensor:
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    return x
+
+
+def attention_forward(q, k, v, mask, bias, scale):
+    """Raw forward on attention-view tensors.  Returns (o, lse)."""
+    lib = _lib.load()
+    B, H, S, R, D = q.shape
+    o = torch.empty((B, H, S, R, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, S, R), dtype=torch.float32, device=q.device)
+    p = _lib.FwdParams()
+    _fill_fwd(p, q, k, v, o, lse, mask, bias, scale)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        _lib.check(lib.evoattn_fwd(C.byref(p), C.c_void_p(stream)), "evoattn_fwd")
+    launches["fwd"] = lib.evoattn_last_launch_count()
+    last_path["fwd"] = lib.evoattn_last_path()
+    return o, lse
+
+
+def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o):
+    """Raw backward on attention-view tensors.  Returns (dq, dk, dv, dbias fp32 or None)."""
+    lib = _lib.load()
+    B, H, S, R, D = q.shape
+    dq = torch.empty((B, H, S, R, D), dtype=q.dtype, device=q.device)
+    dk = torch.empty_like(dq)
+    dv = torch.empty_like(dq)
+    dbias = None if bias is None else torch.empty((B, H, R, R), dtype=torch.float32, device=q.device)
+    p = _lib.BwdParams()
+    _fill_fwd(p.fwd, q, k, v, o, lse, mask, bias, scale)
+    p.d_o, p.dq, p.dk, p.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    p.dbias = None if dbias is None else dbias.data_ptr()
+    p.do_stride, p.dq_stride, p.dk_stride, p.dv_stride = _strides4(d_o), _strides4(dq), _strides4(dk), _strides4(dv)
+    need = lib.evoattn_bwd_workspace_bytes(C.byref(p))
+    ws = torch.empty(max(int(need), 1), dtype=torch.uint8, device=q.device)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), int(need)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        _lib.check(lib.evoattn_bwd(C.byref(p), C.c_void_p(stream)), "evoattn_bwd")
+    launches["bwd"] = lib.evoattn_last_launch_count()
+    last_path["bwd"] = lib.evoattn_last_path()
+    return dq, dk, dv, dbias
+
+
+class _EvoformerAttentionBase(torch.autograd.Function):
+    """Shared implementation; ``layout`` is fixed by the two public subclasses."""
+
+    layout = "reinterpret"
+
+    @classmethod
+    def _forward(cls, ctx, Q, K, V, res_mask, pair_bias):
+        for t in (Q, K, V):
+            _require_cuda(t)
+        if not (Q.shape[-1] == K.shape[-1] == V.shape[-1]):
+            raise AssertionError("Q, K, V must share the head dimension")  # evoformer.py:642-643
+        if Q.dtype not in _DTYPES or K.dtype != Q.dtype or V.dtype != Q.dtype:
+            raise TypeError("Q, K, V must share one dtype out of bfloat16, float16, float32")
+        B, S, R, H, D = Q.shape
+        scale = D ** -0.5  # evoformer.py:646
+        if cls.layout == "reinterpret":
+            Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
+        q, k, v = (_prep_operand(_view_dims(t, cls.layout)) for t in (Q, K, V))
+        mask = None
+        if res_mask is not None:
+            mask = res_mask.reshape(B, S, R)  # [B,S,1,1,R] in the reference (evoformer.py:651)
+            if mask.dtype not in (torch.bool, torch.float32, Q.dtype):
+                mask = mask.to(torch.float32)
+        bias = None
+        if pair_bias is not None:
+            bias = pair_bias.reshape(B, H, R, R)  # [B,1,H,R,R] (evoformer.py:652)
+            if bias.dtype != torch.float32:
+                bias = bias.float()
+            if bias.stride(-1) != 1:
+                bias = bias.contiguous()
+        o, lse = attention_forward(q, k, v, mask, bias, scale)
+        ctx.save_for_backward(q, k, v, mask, bias, o, lse)  # evoformer.py:729
+        ctx.softmax_scale = scale
+        ctx.bias_meta = None if pair_bias is None else (pair_bias.dtype, tuple(pair_bias.shape))
+        return _unview(o, cls.layout)
+
+    @classmethod
+    def _backward(cls, ctx, dO):
+        q, k, v, mask, bias, o, lse = ctx.saved_tensors
+        if cls.layout == "reinterpret":
+            dO = dO.contiguous()  # the reference asserts contiguity instead (evoformer.py:747)
+        d_o = _prep_operand(_view_dims(dO, cls.layout))
+        if d_o.dtype != q.dtype:
+            d_o = d_o.to(q.dtype)
+        dq, dk, dv, dbias = attention_backward(q, k, v, o, lse, mask, bias, ctx.softmax_scale, d_o)
+        d_pair_bias = None
+        if dbias is not None:
+            dtype, shape = ctx.bias_meta
+            # the sum over N_seq stays in fp32 until this single cast (evoformer.py:860 casts to dO's dtype)
+            d_pair_bias = dbias.reshape(shape).to(dtype)
+        return _unview(dq, cls.layout), _unview(dk, cls.layout), _unview(dv, cls.layout), None, d_pair_bias
+
+
+class EvoformerAttention(_EvoformerAttentionBase):
+    """Drop-in for ``evoformer.EvoformerAttention`` (dsevoformer-triton/evoformer.py:633).
+
+    ``EvoformerAttention.apply(Q, K, V, res_mask, pair_bias)`` with
+    Q, K, V ``[B, N_seq, N_res, H, D]``; res_mask ``[B, N_seq, 1, 1, N_res]`` (bool keep-mask,
+    or a floating tensor that is added to the scores); pair_bias ``[B, 1, H, N_res, N_res]``.
+    Like the reference, the head axis is obtained by *reinterpreting* the buffer as
+    ``[B, H, N_seq, N_res, D]``.  Unlike the reference, ``None`` works for the mask and the bias.
+    """
+
+    layout = "reinterpret"
+
+    @staticmethod
+    def forward(ctx, Q, K, V, res_mask=None, pair_bias=None):
+        return EvoformerAttention._forward(ctx, Q, K, V, res_mask, pair_bias)
+
+    @staticmethod
+    def backward(ctx, dO):
+        return EvoformerAttention._backward(ctx, dO)
+
+
+class EvoformerAttentionTrueLayout(_EvoformerAttentionBase):
+    """Same op with genuine head semantics: head h of Q is ``Q[:, :, :, h, :]``
+    (what ``DS4Sci_EvoformerAttention`` computes).  The kernels read the strided view
+    in place through their tensor maps; nothing is transposed in memory."""
+
+    layout = "true"
+
+    @staticmethod
+    def forward(ctx, Q, K, V, res_mask=None, pair_bias=None):
+        return EvoformerAttentionTrueLayout._forward(ctx, Q, K, V, res_mask, pair_bias)
+
+    @staticmethod
+    def backward(ctx, dO):
+        return EvoformerAttentionTrueLayout._backward(ctx, dO)
+
+
+def evoformer_attention(Q, K, V, biases: Optional[Sequence[Optional[torch.Tensor]]] = None, *, layout="true"):
+    """List-style call ``attn(Q, K, V, [res_mask_bias, pair_bias])`` of
+    ``DS4Sci_EvoformerAttention`` (used at dsevoformer-triton/speed_benchmark.py:24,84).
+
+    ``biases[0]`` is the residue mask ``[B, N_seq, 1, 1, N_res]`` (additive when floating,
+    keep-mask when bool); ``biases[1]`` the pair bias ``[B, 1, H, N_res, N_res]``.
+    ``layout="true"`` (default) takes heads from axis 3 as DS4Sci does;
+    ``layout="reinterpret"`` matches ``EvoformerAttention``.
+    """
+    biases = list(biases or [])
+    while len(biases) < 2:
+        biases.append(None)
+    fn = EvoformerAttentionTrueLayout if layout == "true" else EvoformerAttention
+    return fn.apply(Q, K, V, biases[0], biases[1])

@@ -1,0 +1,160 @@
+// extern "C" surface of libevoattn.so: argument validation, dispatch, launches.
+#include <string.h>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace {
+
+thread_local int g_last_path = EVOATTN_PATH_NONE;
+thread_local int g_last_launches = 0;
+
+bool stride_ok16(const int64_t* s, int esize) {
+  for (int i = 0; i < 4; ++i)
+    if ((s[i] * esize) % 16 != 0) return false;
+  return true;
+}
+
+evo::Str4 str4(const int64_t* s) { return evo::Str4{s[0], s[1], s[2], s[3]}; }
+
+int esize_of(int dtype) { return dtype == EVOATTN_FP32 ? 4 : 2; }
+
+int validate_fwd(const evoattn_fwd_params* p) {
+  if (!p) return EVOATTN_ERR_NULL;
+  if (!p->q || !p->k || !p->v || !p->o || !p->lse) return EVOATTN_ERR_NULL;
+  if (p->dtype != EVOATTN_BF16 && p->dtype != EVOATTN_FP16 && p->dtype != EVOATTN_FP32) return EVOATTN_ERR_DTYPE;
+  if (p->B <= 0 || p->H <= 0 || p->S <= 0 || p->R <= 0 || p->D <= 0) return EVOATTN_ERR_SHAPE;
+  if ((long long)p->B * p->H * p->S > 2147483647LL) return EVOATTN_ERR_SHAPE;
+  if (p->R > 65535 * 8) return EVOATTN_ERR_SHAPE;
+  if (p->D > 128) return EVOATTN_ERR_UNSUPPORTED;
+  if (p->mask_kind < EVOATTN_MASK_NONE || p->mask_kind > EVOATTN_MASK_ADD_SAME) return EVOATTN_ERR_DTYPE;
+  if (p->mask_kind != EVOATTN_MASK_NONE && !p->mask) return EVOATTN_ERR_NULL;
+  if (!(p->scale == p->scale)) return EVOATTN_ERR_SHAPE;  // NaN scale
+  return EVOATTN_OK;
+}
+
+void fill_args(const evoattn_fwd_params* p, evo::Args* a) {
+  memset(a, 0, sizeof(*a));
+  a->B = p->B; a->H = p->H; a->S = p->S; a->R = p->R; a->D = p->D;
+  a->scale = p->scale;
+  a->q = p->q; a->k = p->k; a->v = p->v; a->o = p->o; a->lse = p->lse;
+  a->sq = str4(p->q_stride); a->sk = str4(p->k_stride); a->sv = str4(p->v_stride); a->so = str4(p->o_stride);
+  a->mask = p->mask_kind == EVOATTN_MASK_NONE ? nullptr : p->mask;
+  a->mask_kind = p->mask_kind;
+  a->smask = evo::Str3{p->mask_stride[0], p->mask_stride[1], p->mask_stride[2]};
+  a->bias = p->bias;
+  a->sbias = evo::Str3{p->bias_stride[0], p->bias_stride[1], p->bias_stride[2]};
+  a->status = p->status;
+}
+
+int validate_bwd(const evoattn_bwd_params* p) {
+  if (!p) return EVOATTN_ERR_NULL;
+  int rc = validate_fwd(&p->fwd);
+  if (rc) return rc;
+  if (!p->d_o || !p->dq || !p->dk || !p->dv) return EVOATTN_ERR_NULL;
+  if (p->fwd.bias && !p->dbias) return EVOATTN_ERR_NULL;
+  return EVOATTN_OK;
+}
+
+void fill_bwd_args(const evoattn_bwd_params* p, evo::Args* a) {
+  fill_args(&p->fwd, a);
+  a->d_o = p->d_o; a->dq = p->dq; a->dk = p->dk; a->dv = p->dv;
+  a->dbias = p->fwd.bias ? p->dbias : nullptr;
+  a->sdo = str4(p->do_stride); a->sdq = str4(p->dq_stride); a->sdk = str4(p->dk_stride); a->sdv = str4(p->dv_stride);
+}
+
+size_t generic_bwd_workspace(const evo::Args& a) {
+  return (size_t)a.B * a.H * a.S * a.R * sizeof(float);  // delta
+}
+
+bool use_sm100_fwd(const evoattn_fwd_params* p, const evo::Args& a) {
+  if (p->flags & EVOATTN_FLAG_FORCE_GENERIC) return false;
+  if (p->dtype == EVOATTN_FP32) return false;
+  if (((uintptr_t)p->q | (uintptr_t)p->k | (uintptr_t)p->v | (uintptr_t)p->o) & 15) return false;
+  const int es = esize_of(p->dtype);
+  if (!stride_ok16(p->q_stride, es) || !stride_ok16(p->k_stride, es) || !stride_ok16(p->v_stride, es) ||
+      !stride_ok16(p->o_stride, es))
+    return false;
+  return evo::sm100_fwd_supported(p->dtype, a);
+}
+
+bool use_sm100_bwd(const evoattn_bwd_params* p, const evo::Args& a) {
+  if (!use_sm100_fwd(&p->fwd, a)) return false;
+  if (((uintptr_t)p->d_o | (uintptr_t)p->dq | (uintptr_t)p->dk | (uintptr_t)p->dv) & 15) return false;
+  const int es = esize_of(p->fwd.dtype);
+  if (!stride_ok16(p->do_stride, es) || !stride_ok16(p->dq_stride, es) || !stride_ok16(p->dk_stride, es) ||
+      !stride_ok16(p->dv_stride, es))
+    return false;
+  return evo::sm100_bwd_supported(p->fwd.dtype, a);
+}
+
+}  // namespace
+
+extern "C" {
+
+int evoattn_abi_version(void) { return EVOATTN_ABI_VERSION; }
+
+const char* evoattn_strerror(int status) {
+  switch (status) {
+    case EVOATTN_OK: return "ok";
+    case EVOATTN_ERR_NULL: return "a required pointer is null";
+    case EVOATTN_ERR_SHAPE: return "a dimension or scale is out of range";
+    case EVOATTN_ERR_DTYPE: return "unknown dtype or mask kind";
+    case EVOATTN_ERR_ALIGN: return "base address or stride is not 16-byte aligned";
+    case EVOATTN_ERR_UNSUPPORTED: return "no kernel covers this request (head dimension above 128?)";
+    case EVOATTN_ERR_CUDA: return "a CUDA call failed (launch or tensor-map creation)";
+    case EVOATTN_ERR_WORKSPACE: return "workspace is null or smaller than evoattn_bwd_workspace_bytes()";
+    case EVOATTN_ERR_DEVICE: return "a kernel gave up a bounded wait and set the device status word";
+    default: return "unknown status";
+  }
+}
+
+int evoattn_fwd(const evoattn_fwd_params* p, void* cuda_stream) {
+  g_last_path = EVOATTN_PATH_NONE;
+  g_last_launches = 0;
+  int rc = validate_fwd(p);
+  if (rc) return rc;
+  evo::Args a;
+  fill_args(p, &a);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  if (use_sm100_fwd(p, a)) {
+    g_last_path = EVOATTN_PATH_TCGEN05;
+    return evo::launch_sm100_fwd(p->dtype, a, st, &g_last_launches);
+  }
+  g_last_path = EVOATTN_PATH_GENERIC;
+  return evo::launch_generic_fwd(p->dtype, a, st, &g_last_launches) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+}
+
+size_t evoattn_bwd_workspace_bytes(const evoattn_bwd_params* p) {
+  if (validate_bwd(p)) return 0;
+  evo::Args a;
+  fill_bwd_args(p, &a);
+  if (use_sm100_bwd(p, a)) return evo::sm100_bwd_workspace_bytes(p->fwd.dtype, a);
+  return generic_bwd_workspace(a);
+}
+
+int evoattn_bwd(const evoattn_bwd_params* p, void* cuda_stream) {
+  g_last_path = EVOATTN_PATH_NONE;
+  g_last_launches = 0;
+  int rc = validate_bwd(p);
+  if (rc) return rc;
+  evo::Args a;
+  fill_bwd_args(p, &a);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  const bool fast = use_sm100_bwd(p, a);
+  const size_t need = fast ? evo::sm100_bwd_workspace_bytes(p->fwd.dtype, a) : generic_bwd_workspace(a);
+  if (need && (!p->workspace || p->workspace_bytes < need)) return EVOATTN_ERR_WORKSPACE;
+  if (need && ((uintptr_t)p->workspace & 255)) return EVOATTN_ERR_ALIGN;
+  if (fast) {
+    g_last_path = EVOATTN_PATH_TCGEN05;
+    return evo::launch_sm100_bwd(p->fwd.dtype, a, p->workspace, p->workspace_bytes, st, &g_last_launches);
+  }
+  g_last_path = EVOATTN_PATH_GENERIC;
+  a.delta = reinterpret_cast<float*>(p->workspace);
+  return evo::launch_generic_bwd(p->fwd.dtype, a, st, &g_last_launches) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+}
+
+int evoattn_last_path(void) { return g_last_path; }
+int evoattn_last_launch_count(void) { return g_last_launches; }
+
+}  // extern "C"

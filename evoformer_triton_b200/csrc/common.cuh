@@ -1,0 +1,96 @@
+// Shared device-side definitions for the Evoformer attention kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "evoattn.h"
+
+namespace evo {
+
+// Device status codes written to evoattn_fwd_params::status.
+enum : int {
+  DEV_OK = 0,
+  DEV_TIMEOUT_TMA = 1,   // a wait for a TMA copy ran out
+  DEV_TIMEOUT_MMA = 2,   // a wait for tcgen05.commit ran out
+  DEV_TIMEOUT_SYNC = 3   // a wait between warps ran out
+};
+
+struct Str4 {
+  long long b, h, s, r;
+};
+struct Str3 {
+  long long a, b, c;
+};
+
+// Kernel arguments (by value).  Attention view [B,H,S,R,D]; D contiguous.
+struct Args {
+  int B, H, S, R, D;
+  float scale;
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;          // forward: out; backward: in
+  float* lse;       // [B,H,S,R]
+  Str4 sq, sk, sv, so;
+  const void* mask; // [B,S,R]
+  int mask_kind;
+  Str3 smask;       // (b,s,r)
+  const float* bias;  // [B,H,R,R]
+  Str3 sbias;         // (b,h,i)
+  // backward only
+  const void* d_o;
+  void* dq;
+  void* dk;
+  void* dv;
+  float* dbias;     // [B,H,R,R] contiguous
+  float* delta;     // [B,H,S,R] (workspace)
+  Str4 sdo, sdq, sdk, sdv;
+  int* status;
+};
+
+template <class T> __device__ __forceinline__ float to_float(T x);
+template <> __device__ __forceinline__ float to_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
+
+template <class T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+
+__device__ __forceinline__ long long off4(const Str4& s, int b, int h, int ss, int r) {
+  return (long long)b * s.b + (long long)h * s.h + (long long)ss * s.s + (long long)r * s.r;
+}
+
+// Residue mask applied to one score.  BOOL replaces (evoformer.py:69), the others add.
+template <class T>
+__device__ __forceinline__ float apply_mask(float x, const void* mask, int kind, long long idx, bool& replaced) {
+  replaced = false;
+  if (kind == EVOATTN_MASK_BOOL) {
+    if (reinterpret_cast<const unsigned char*>(mask)[idx] == 0) {
+      replaced = true;
+      return -FLT_MAX;
+    }
+    return x;
+  }
+  if (kind == EVOATTN_MASK_ADD_F32) return x + reinterpret_cast<const float*>(mask)[idx];
+  if (kind == EVOATTN_MASK_ADD_SAME) return x + to_float<T>(reinterpret_cast<const T*>(mask)[idx]);
+  return x;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+}  // namespace evo

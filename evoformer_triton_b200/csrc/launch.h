@@ -1,0 +1,23 @@
+// Host-side launch entry points of the kernel families (internal to the library).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include "common.cuh"
+
+namespace evo {
+
+// CUDA-core kernels (generic_kernels.cu).  Backward needs a.delta = [B,H,S,R] fp32 scratch.
+cudaError_t launch_generic_fwd(int dtype, const Args& a, cudaStream_t st, int* launches);
+cudaError_t launch_generic_bwd(int dtype, const Args& a, cudaStream_t st, int* launches);
+
+// tcgen05 / TMEM / TMA kernels (fwd_sm100.cu, bwd_sm100.cu).  The *_supported
+// predicates say whether a request is covered; the launchers return an EVOATTN_* status.
+bool sm100_fwd_supported(int dtype, const Args& a);
+int launch_sm100_fwd(int dtype, const Args& a, cudaStream_t st, int* launches);
+bool sm100_bwd_supported(int dtype, const Args& a);
+size_t sm100_bwd_workspace_bytes(int dtype, const Args& a);
+int launch_sm100_bwd(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
+                     int* launches);
+
+}  // namespace evo

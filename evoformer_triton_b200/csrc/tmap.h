@@ -1,0 +1,21 @@
+// Host-side construction of TMA tensor maps (cuTensorMapEncodeTiled through the
+// runtime's driver entry point lookup, so the library does not link libcuda).
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace evo {
+
+// 16-bit [B,H,S,R,D] attention-view tensor -> 5-D map with dims (D, R, S, H, B).
+// Box = (box_d, box_r, 1, 1, 1); rows of box_d*2 bytes are swizzled with the matching
+// 32/64/128-byte pattern.  Elements beyond D or R read as zero.
+bool make_qkv_map(CUtensorMap* out, const void* base, const Str4& stride_elems, int B, int H, int S, int R, int D,
+                  int box_d, int box_r);
+
+// fp32 [B,H,R,R] pair bias -> 4-D map with dims (R_j, R_i, H, B); box = (32, box_i, 1, 1),
+// 128-byte swizzle (one row of a box is 32 floats = 128 bytes).
+bool make_bias_map(CUtensorMap* out, const float* base, const Str3& stride_elems, int B, int H, int R, int box_i);
+
+}  // namespace evo

@@ -1,0 +1,134 @@
+/*
+ * evoattn.h - C ABI of libevoattn.so: Evoformer attention (pair-bias + residue-mask
+ * flash attention, forward and backward) for NVIDIA B200 (sm_100a).
+ *
+ * Plain C, plain pointers and sizes.  The library owns no memory: every input,
+ * output and scratch buffer is device memory allocated by the caller.  All work is
+ * enqueued on the CUDA stream handed in (a cudaStream_t passed as void*); nothing
+ * synchronises, nothing is freed, no pointer is kept after a call returns.
+ *
+ * Tensors are described in the *attention view* [B, H, S, R, D]:
+ *   B batch, H heads, S = N_seq (MSA rows), R = N_res, D = head dimension.
+ * The reference obtains this view by reinterpreting its [B, N_seq, N_res, H, D]
+ * tensors (dsevoformer-triton/evoformer.py:648-650); a caller that wants true head
+ * semantics passes the strides of a permuted view instead.  Strides are in elements,
+ * for the axes (b, h, s, r); the D axis is contiguous.
+ */
+#ifndef EVOATTN_H_
+#define EVOATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EVOATTN_ABI_VERSION 1
+
+/* status codes (0 = success). */
+enum {
+  EVOATTN_OK = 0,
+  EVOATTN_ERR_NULL = 1,        /* a required pointer is null */
+  EVOATTN_ERR_SHAPE = 2,       /* a dimension is out of range */
+  EVOATTN_ERR_DTYPE = 3,       /* unknown dtype / mask kind */
+  EVOATTN_ERR_ALIGN = 4,       /* base address or stride breaks the 16-byte rule */
+  EVOATTN_ERR_UNSUPPORTED = 5, /* valid request that no kernel covers */
+  EVOATTN_ERR_CUDA = 6,        /* a CUDA call (launch, tensor map) failed */
+  EVOATTN_ERR_WORKSPACE = 7,   /* workspace missing or too small */
+  EVOATTN_ERR_DEVICE = 8       /* the device status word was set by a kernel */
+};
+
+enum { EVOATTN_BF16 = 0, EVOATTN_FP16 = 1, EVOATTN_FP32 = 2 };
+
+/* res_mask forms.  BOOL: one byte per key, non-zero = keep; dropped keys have their
+ * score *replaced* by -FLT_MAX (evoformer.py:69, test.py:54).  The additive forms add
+ * the value to the score (the DS4Sci "mask bias" convention). */
+enum {
+  EVOATTN_MASK_NONE = 0,
+  EVOATTN_MASK_BOOL = 1,
+  EVOATTN_MASK_ADD_F32 = 2,
+  EVOATTN_MASK_ADD_SAME = 3 /* additive, stored in the q/k/v dtype */
+};
+
+/* flags */
+enum {
+  EVOATTN_FLAG_FORCE_GENERIC = 1 /* use the CUDA-core kernels even where a tcgen05 kernel exists */
+};
+
+/* Which kernel family served the last call on this thread (for tests and logs). */
+enum { EVOATTN_PATH_NONE = 0, EVOATTN_PATH_GENERIC = 1, EVOATTN_PATH_TCGEN05 = 2 };
+
+typedef struct evoattn_fwd_params {
+  int32_t dtype;          /* EVOATTN_BF16 / FP16 / FP32: type of q, k, v, o */
+  int32_t B, H, S, R, D;
+  float scale;            /* softmax scale, D^-1/2 in the reference (evoformer.py:646) */
+  uint32_t flags;
+  const void* q;          /* [B,H,S,R,D] attention view */
+  const void* k;
+  const void* v;
+  void* o;                /* out, same dtype */
+  float* lse;             /* out, contiguous [B,H,S,R] fp32: log-sum-exp of each score row
+                             (the tensor M of evoformer.py:669-671) */
+  int64_t q_stride[4];    /* element strides of (b,h,s,r) */
+  int64_t k_stride[4];
+  int64_t v_stride[4];
+  int64_t o_stride[4];
+  const void* mask;       /* [B,S,R] or null */
+  int32_t mask_kind;
+  int32_t reserved0;
+  int64_t mask_stride[3]; /* element strides of (b,s,r) */
+  const float* bias;      /* pair bias [B,H,R,R] fp32 or null; last axis contiguous */
+  int64_t bias_stride[3]; /* element strides of (b,h,i) */
+  int32_t* status;        /* optional device word; a kernel that gives up a bounded wait
+                             writes a non-zero code here instead of hanging or trapping */
+} evoattn_fwd_params;
+
+typedef struct evoattn_bwd_params {
+  evoattn_fwd_params fwd; /* same q,k,v,o,lse,mask,bias as the forward call (o and lse are inputs) */
+  const void* d_o;        /* dO, attention view */
+  void* dq;               /* out */
+  void* dk;               /* out */
+  void* dv;               /* out */
+  float* dbias;           /* out, fp32 [B,H,R,R] contiguous, or null when bias is null.
+                             Written in full (no need to zero it first):
+                             the sum over the S rows of dS (evoformer.py:458) */
+  int64_t do_stride[4];
+  int64_t dq_stride[4];
+  int64_t dk_stride[4];
+  int64_t dv_stride[4];
+  void* workspace;        /* device scratch of at least evoattn_bwd_workspace_bytes() */
+  size_t workspace_bytes;
+} evoattn_bwd_params;
+
+/* ABI version of the loaded library; compare with EVOATTN_ABI_VERSION. */
+int evoattn_abi_version(void);
+
+/* Human-readable text of a status code.  Never null. */
+const char* evoattn_strerror(int status);
+
+/* Forward pass.  Replaces the device side of EvoformerAttention.forward
+ * (dsevoformer-triton/evoformer.py:635-737: the _attn_fwd launch at :676-724,
+ * kernel at :103-297). */
+int evoattn_fwd(const evoattn_fwd_params* p, void* cuda_stream);
+
+/* Bytes of device scratch evoattn_bwd needs for these shapes (may be 0).
+ * The reference allocates its scratch (delta, fp32 d_pair_bias) inside backward
+ * (evoformer.py:749-758); here the caller does. */
+size_t evoattn_bwd_workspace_bytes(const evoattn_bwd_params* p);
+
+/* Backward pass.  Replaces the device side of EvoformerAttention.backward
+ * (evoformer.py:741-862: _attn_bwd_preprocess :299-326, _attn_bwd_dk_dv :479-630,
+ * _attn_bwd_dq :329-476). */
+int evoattn_bwd(const evoattn_bwd_params* p, void* cuda_stream);
+
+/* EVOATTN_PATH_* of the most recent forward / backward call made by this thread. */
+int evoattn_last_path(void);
+
+/* Number of kernels the most recent forward / backward call of this thread launched. */
+int evoattn_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EVOATTN_H_ */
