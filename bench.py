@@ -124,7 +124,7 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": str(w.dtype).split(".")[-1], "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": dtype_name(w.dtype), "data": "synthetic",
         "config": {"workload": describe(w), "sample": f"{rows} of {w.S} MSA rows per step"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": f"{rows} of {w.S} MSA rows, fwd+bwd, torch CPU {torch.get_num_threads()} threads"},
@@ -133,9 +133,13 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def dtype_name(dt):
+    return {"bfloat16": "bf16", "float16": "fp16", "float32": "fp32"}[str(dt).split(".")[-1]]
+
+
 def describe(w):
     return (f"{w.name}: {w.what}; B={w.B} N_seq={w.S} N_res={w.R} H={w.H} D={w.D} "
-            f"{str(w.dtype).split('.')[-1]} fwd+bwd")
+            f"{dtype_name(w.dtype)} fwd+bwd")
 
 
 def main():
@@ -305,7 +309,7 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": str(w.dtype).split(".")[-1], "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": dtype_name(w.dtype), "data": "synthetic",
             "config": {"workload": describe(w), "rows_per_gpu": w.S, "global_rows": w.S * world,
                        "l2": "256 MB buffer written between timed steps",
                        "collective": "NCCL all-reduce of d(pair_bias) inside the step" if world > 1 else "none",

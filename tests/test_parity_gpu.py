@@ -140,7 +140,7 @@ def test_shapes_default_path(cfg):
     got, paths = run_op(x)
     print("paths", paths)
     if R % 4 == 0:
-        assert paths[0] == _lib().PATH_TCGEN05
+        assert paths == (_lib().PATH_TCGEN05, _lib().PATH_TCGEN05)
     check(got, x, label=f"{cfg} ")
 
 
@@ -166,12 +166,22 @@ def test_fully_masked_row_default_path():
     check(got, x, label="dead-row ")
 
 
-def test_runs_are_bitwise_reproducible():
-    x = rand_inputs(1, 4, 384, 2, 32, torch.bfloat16, seed=3)
+def test_runs_are_reproducible():
+    """O, dK, dV have a fixed summation order: bitwise equal between runs.  dQ and
+    d(pair_bias) are summed across CTAs by fp32 reductions whose order is not fixed (the
+    reference's atomics, evoformer.py:458, are not either): equal to rounding."""
+    x = rand_inputs(1, 6, 384, 2, 32, torch.bfloat16, seed=3)
     a, _ = run_op(x)
     b, _ = run_op(x)
     for name, u, v in zip(NAMES, a, b):
-        assert torch.equal(u, v), f"{name} changed between two identical runs"
+        if name in ("O", "dK", "dV"):
+            assert torch.equal(u, v), f"{name} changed between two identical runs"
+        else:
+            assert oc.rel_err(u, v) < 4e-3, name
+    a, _ = run_op(x, generic=True)
+    b, _ = run_op(x, generic=True)
+    for name, u, v in zip(NAMES, a, b):
+        assert torch.equal(u, v), f"cuda-core {name} changed between two identical runs"
 
 
 @pytest.mark.parametrize("name", ["C2"])
