@@ -64,7 +64,7 @@ class _SumGradAcrossRanks(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous()
-        if g.dtype != torch.float32:
+        if g.dtype in (torch.bfloat16, torch.float16):  # sum in fp32, never in a 16-bit type
             g32 = g.float()
             dist.all_reduce(g32, op=dist.ReduceOp.SUM, group=ctx.group)
             return g32.to(g.dtype), None

@@ -211,3 +211,39 @@ def test_full_size_properties_c5_rows():
     x2["V"] = (x["V"].float() * 2).to(x["V"].dtype)
     b, _ = run_op(x2)
     assert oc.rel_err(b[0], 2 * a[0].float()) < 1e-2
+
+
+# The reference's own shape matrix (test.py:82-101), (BATCH, HEAD, N_SEQ, SEQ_LEN, DIM), duplicates removed.
+REFERENCE_SHAPES = [
+    (1, 16, 1, 128, 64), (1, 4, 128, 128, 32), (5, 10, 200, 384, 64), (10, 5, 200, 384, 64),
+    (1, 10, 200, 640, 64), (1, 15, 200, 640, 64), (1, 5, 100, 768, 64), (1, 10, 100, 768, 64),
+    (1, 1, 100, 1280, 64), (1, 5, 300, 512, 64), (1, 5, 300, 384, 64),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("shape", REFERENCE_SHAPES, ids=lambda s: "B%dH%dS%dR%dD%d" % s)
+def test_reference_shape_matrix(shape, dtype):
+    """test.py:13-80 restated: same shapes, same input distributions, same acceptance.  At these
+    sizes the naive path is evaluated with the oracle code on the GPU (the reference runs its
+    naive path on the GPU as well), chunked over MSA rows."""
+    import evoformer_triton_b200 as evo
+    B, H, S, R, D = shape
+    if dtype == torch.float16 and B * H * S * R > 4_000_000:
+        pytest.skip("fp16 repeats only the smaller shapes")
+    g = torch.Generator(device=DEV).manual_seed(B * 1000 + H * 100 + S + R)
+    shp = (B, S, R, H, D)
+    mk = lambda std: (torch.randn(shp, generator=g, device=DEV) * std).to(dtype)  # noqa: E731
+    Q, K, V = mk(0.5), mk(0.5), mk(0.5)
+    res_mask = torch.randint(0, 2, (B, S, 1, 1, R), generator=g, device=DEV, dtype=torch.int32).bool()
+    pair_bias = torch.randn((B, 1, H, R, R), generator=g, device=DEV) * 0.5
+    dO = torch.randn(shp, generator=g, device=DEV).to(dtype)
+    ref = oc.attention_fwd_bwd(Q, K, V, res_mask, pair_bias, dO, chunk=max(1, 2_000_000_000 // (B * H * R * R * 16)))
+    q, k, v, b = Q.clone().requires_grad_(), K.clone().requires_grad_(), V.clone().requires_grad_(), \
+        pair_bias.clone().requires_grad_()
+    out = evo.EvoformerAttention.apply(q, k, v, res_mask, b)
+    out.backward(dO)
+    torch.cuda.synchronize()
+    evo.check_device_status()
+    for name, got, want in zip(NAMES, (out, q.grad, k.grad, v.grad, b.grad), ref):
+        assert reference_allclose(got, want, dtype), f"{name} fails the reference's allclose at {shape}"
