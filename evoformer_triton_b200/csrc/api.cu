@@ -8,6 +8,17 @@ namespace {
 
 thread_local int g_last_path = EVOATTN_PATH_NONE;
 thread_local int g_last_launches = 0;
+thread_local bool g_ctx_bound = false;
+
+// Tensor maps are encoded through the driver API, which needs the device's primary context
+// to be current on the calling thread.  A thread that has made no runtime call yet (PyTorch's
+// autograd worker on its first backward) gets it bound here, once.
+void bind_context_once() {
+  if (!g_ctx_bound) {
+    cudaFree(nullptr);  // the customary no-op that initialises / binds the primary context
+    g_ctx_bound = true;
+  }
+}
 
 bool stride_ok16(const int64_t* s, int esize) {
   for (int i = 0; i < 4; ++i)
@@ -117,6 +128,7 @@ int evoattn_fwd(const evoattn_fwd_params* p, void* cuda_stream) {
   evo::Args a;
   fill_args(p, &a);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  bind_context_once();
   if (use_sm100_fwd(p, a)) {
     g_last_path = EVOATTN_PATH_TCGEN05;
     return evo::launch_sm100_fwd(p->dtype, a, st, &g_last_launches);
@@ -141,6 +153,7 @@ int evoattn_bwd(const evoattn_bwd_params* p, void* cuda_stream) {
   evo::Args a;
   fill_bwd_args(p, &a);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  bind_context_once();
   const bool fast = use_sm100_bwd(p, a);
   const size_t need = fast ? evo::sm100_bwd_workspace_bytes(p->fwd.dtype, a) : generic_bwd_workspace(a);
   if (need && (!p->workspace || p->workspace_bytes < need)) return EVOATTN_ERR_WORKSPACE;

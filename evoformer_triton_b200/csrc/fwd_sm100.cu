@@ -5,15 +5,21 @@
 // (_attn_fwd) compute:  O = softmax(scale*Q K^T + bias, masked) V  and the row
 // log-sum-exp, without ever writing the R x R scores to memory.
 //
-// One CTA = one 128-row query tile of one (b,h,s) slab, 256 threads:
-//   * thread 0 issues the TMA loads of Q, K, V and all tcgen05.mma instructions;
-//   * all 8 warps run the softmax: thread (warp w, lane l) owns score row 32*(w%4)+l
-//     (= its TMEM lane) and the 64 columns of half w/4 of each 128-key tile;
-//   * S = Q K^T lands in TMEM columns [0,128); P (rounded to the storage type, as
-//     evoformer.py:84 does) goes to shared memory in the K-major 128B-swizzled layout
-//     and P V lands in TMEM columns [128,128+DP); the running O lives in registers.
-//   * the pair-bias tile arrives by TMA in 128x32 fp32 chunks (128B swizzle) so that a
-//     thread can read "its" row with conflict-free 16-byte shared loads.
+// Persistent, warp-specialised kernel, one CTA per SM, 384 threads:
+//   warp 0      TMA producer: Q tiles, K/V tiles (64 keys each) and pair-bias tiles
+//   warp 1      issues every tcgen05.mma
+//   warps 4-7   softmax warpgroup A        warps 8-11   softmax warpgroup B
+// A work item is one 128-row query tile of TWO consecutive MSA rows s of one (b,h):
+// warpgroup A takes row 2p, B takes row 2p+1.  Both rows use the same pair-bias tile, so
+// it is staged in shared memory once per item pair.  Inside a warpgroup thread t owns
+// score row t (= TMEM lane t) and all 64 columns of the current key tile, so the row
+// maximum and sum need no exchange between threads.
+//
+// Per warpgroup and key tile n:  S_n = Q K_n^T lands in TMEM (double buffered); the
+// warpgroup turns it into P_n (rounded to the storage type as evoformer.py:84 does) in
+// shared memory; P_n V_n lands in a second TMEM double buffer and is folded into the
+// fp32 output accumulator in registers one tile later, scaled by the softmax correction
+// of that tile.  The MMA warp runs S_{n+1} while the warpgroup is busy with tile n.
 #include <type_traits>
 
 #include "common.cuh"
@@ -26,29 +32,36 @@ namespace {
 
 using namespace ptx;
 
-constexpr int BM = 128;        // query rows per CTA
-constexpr int BN = 128;        // keys per tile
-constexpr int kThreads = 256;
-constexpr int kTmemCols = 256; // S [0,128) + PV [128,128+DP)
+constexpr int BM = 128;  // query rows per warpgroup tile
+constexpr int BN = 64;   // keys per tile
+constexpr int kThreads = 384;
+constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int MASK_MIN = 0;    // boolean keep-mask (or none): score = min(score, m) with m = +-FLT_MAX
-constexpr int MASK_ADD = 1;    // additive mask
+constexpr int MASK_MIN = 0;  // boolean keep-mask (or none): score = min(score, m), m = +-FLT_MAX
+constexpr int MASK_ADD = 1;  // additive mask
 
 template <int DP>
-struct FwdSmem {
-  static constexpr int RB = DP * 2;            // bytes per staged Q/K/V row
-  static constexpr int kTile = BM * RB;        // bytes per Q/K/V tile
-  static constexpr int kP = BM * BN * 2;       // 32 KB
-  static constexpr int kBiasChunk = BM * 128;  // 128 rows x 32 fp32
+struct Cfg {
+  static constexpr int RB = DP * 2;                    // bytes per staged row
+  static constexpr int QST = (DP == 64) ? 1 : 2;       // Q stages per warpgroup
+  static constexpr int NKV = (DP == 64) ? 2 : 4;       // K and V ring depth per warpgroup
+  static constexpr int BST = 2;                        // pair-bias stages (shared by both warpgroups)
+  static constexpr int kQ = BM * RB;
+  static constexpr int kKV = BN * RB;
+  static constexpr int kP = BM * BN * 2;               // 16 KB
+  static constexpr int kBias = BM * BN * 4;            // 32 KB = two 128x32 fp32 boxes
   static constexpr int offQ = 0;
-  static constexpr int offK = offQ + kTile;
-  static constexpr int offV = offK + kTile;
-  static constexpr int offP = offV + kTile;
-  static constexpr int offB = offP + kP;       // two chunk buffers, one per warpgroup
-  static constexpr int offMask = offB + 2 * kBiasChunk;
+  static constexpr int offK = offQ + 2 * QST * kQ;
+  static constexpr int offV = offK + 2 * NKV * kKV;
+  static constexpr int offP = offV + 2 * NKV * kKV;
+  static constexpr int offB = offP + 2 * kP;
+  static constexpr int offMask = offB + BST * kBias;
+  static constexpr int kNumBars = 2 * (2 * QST + 4 * NKV + 2 + 1 + 2) + 2 * BST;
   static size_t bytes(int r_pad) {
-    return (size_t)offMask + (size_t)r_pad * 4 /*mask*/ + 4 * BM * 4 /*pmax,psum*/ + 128 /*barriers*/ + 1024 /*align*/;
+    return (size_t)offMask + (size_t)2 * r_pad * 4 + kNumBars * 8 + 64 + 1024;
   }
+  // TMEM columns of warpgroup w: S double buffer, then PV double buffer
+  static constexpr int tmemWg = 2 * BN + 2 * DP;
 };
 
 template <class T> struct Pack2;
@@ -65,50 +78,60 @@ template <> struct Pack2<__half> {
   }
 };
 
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+struct Item {
+  int b, h, qt, sp;
+};
+__device__ __forceinline__ Item decode_item(int idx, int NSP, int NQT, int H) {
+  Item it;
+  it.sp = idx % NSP; idx /= NSP;
+  it.qt = idx % NQT; idx /= NQT;
+  it.h = idx % H;
+  it.b = idx / H;
+  return it;
+}
+
 template <class T, int DP, int MASKMODE>
 __global__ void __launch_bounds__(kThreads, 1)
-evo_fwd_sm100_kernel(const Args a, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB) {
-  using L = FwdSmem<DP>;
-  constexpr int RB = L::RB;
+evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CUtensorMap tmQ,
+                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                     const __grid_constant__ CUtensorMap tmB) {
+  using C = Cfg<DP>;
+  constexpr int RB = C::RB, QST = C::QST, NKV = C::NKV, BST = C::BST;
   constexpr uint32_t SWZ = swizzle_code_for_row_bytes(RB);
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-  constexpr int HALF_D = DP / 2;  // PV columns each thread accumulates
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem + L::offQ;
-  uint8_t* sK = smem + L::offK;
-  uint8_t* sV = smem + L::offV;
-  uint8_t* sP = smem + L::offP;
-  uint8_t* sB = smem + L::offB;
-  float* sMask = reinterpret_cast<float*>(smem + L::offMask);
-  const int NT = (a.R + BN - 1) / BN;
-  const int r_pad = NT * BN;
-  float* sPmax = sMask + r_pad;          // [2][BM]
-  float* sPsum = sPmax + 2 * BM;         // [2][BM]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sPsum + 2 * BM);
-  uint64_t* bar_q = bars + 0;
-  uint64_t* bar_k = bars + 1;
-  uint64_t* bar_v = bars + 2;
-  uint64_t* bar_s = bars + 3;
-  uint64_t* bar_o = bars + 4;
-  uint64_t* bar_b = bars + 5;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 9);
+  const int T_TILES = (a.R + BN - 1) / BN;
+  const int r_pad = T_TILES * BN;
+  float* sMask = reinterpret_cast<float*>(smem + C::offMask);  // [2][r_pad]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sMask + 2 * r_pad);
+  // barrier layout: per warpgroup w a block of PER, then the shared bias barriers
+  constexpr int PER = 2 * QST + 4 * NKV + 2 + 1 + 2;
+  auto q_full = [&](int w, int st) { return bars + w * PER + st; };
+  auto q_empty = [&](int w, int st) { return bars + w * PER + QST + st; };
+  auto k_full = [&](int w, int st) { return bars + w * PER + 2 * QST + st; };
+  auto k_empty = [&](int w, int st) { return bars + w * PER + 2 * QST + NKV + st; };
+  auto v_full = [&](int w, int st) { return bars + w * PER + 2 * QST + 2 * NKV + st; };
+  auto v_empty = [&](int w, int st) { return bars + w * PER + 2 * QST + 3 * NKV + st; };
+  auto s_full = [&](int w, int i) { return bars + w * PER + 2 * QST + 4 * NKV + i; };
+  auto p_full = [&](int w) { return bars + w * PER + 2 * QST + 4 * NKV + 2; };
+  auto o_full = [&](int w, int i) { return bars + w * PER + 2 * QST + 4 * NKV + 3 + i; };
+  auto b_full = [&](int st) { return bars + 2 * PER + st; };
+  auto b_empty = [&](int st) { return bars + 2 * PER + BST + st; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + C::kNumBars + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wg = warp >> 2;                  // column half
-  const int row = (warp & 3) * 32 + lane;    // score row inside the tile == TMEM lane
-
-  // CTA -> (b, h, q-tile, s); s fastest so neighbouring CTAs share the same bias rows in L2.
   const int NQT = (a.R + BM - 1) / BM;
-  int idx = blockIdx.x;
-  const int s = idx % a.S; idx /= a.S;
-  const int qt = idx % NQT; idx /= NQT;
-  const int h = idx % a.H;
-  const int b = idx / a.H;
-  const int i0 = qt * BM;
+  const int NSP = (a.S + 1) / 2;
   const bool has_bias = a.bias != nullptr;
 
   // A launch that follows a failed one returns at once (one reader, so the CTA agrees).
@@ -117,8 +140,17 @@ evo_fwd_sm100_kernel(const Args a, const __grid_constant__ CUtensorMap tmQ, cons
   if (*abort_flag) return;
 
   if (tid == 0) {
-    mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1); mbar_init(bar_s, 1); mbar_init(bar_o, 1);
-    mbar_init(bar_b + 0, 1); mbar_init(bar_b + 1, 1);
+    for (int w = 0; w < 2; ++w) {
+      for (int st = 0; st < QST; ++st) { mbar_init(q_full(w, st), 1); mbar_init(q_empty(w, st), 1); }
+      for (int st = 0; st < NKV; ++st) {
+        mbar_init(k_full(w, st), 1); mbar_init(k_empty(w, st), 1);
+        mbar_init(v_full(w, st), 1); mbar_init(v_empty(w, st), 1);
+      }
+      mbar_init(s_full(w, 0), 1); mbar_init(s_full(w, 1), 1);
+      mbar_init(p_full(w), 128);
+      mbar_init(o_full(w, 0), 1); mbar_init(o_full(w, 1), 1);
+    }
+    for (int st = 0; st < BST; ++st) { mbar_init(b_full(st), 1); mbar_init(b_empty(st), 256); }
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
     if (has_bias) prefetch_tmap(&tmB);
@@ -127,226 +159,274 @@ evo_fwd_sm100_kernel(const Args a, const __grid_constant__ CUtensorMap tmQ, cons
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
-  // Mask row of this (b, s) as one float per key.  Keys beyond R are always excluded.
-  for (int j = tid; j < r_pad; j += kThreads) {
-    float m;
-    if (j >= a.R) {
-      m = -FLT_MAX;
-    } else if (a.mask_kind == EVOATTN_MASK_NONE) {
-      m = (MASKMODE == MASK_MIN) ? FLT_MAX : 0.f;
-    } else {
-      const long long mi = (long long)b * a.smask.a + (long long)s * a.smask.b + (long long)j * a.smask.c;
-      if (MASKMODE == MASK_MIN) m = reinterpret_cast<const unsigned char*>(a.mask)[mi] ? FLT_MAX : -FLT_MAX;
-      else if (a.mask_kind == EVOATTN_MASK_ADD_F32) m = reinterpret_cast<const float*>(a.mask)[mi];
-      else m = to_float<T>(reinterpret_cast<const T*>(a.mask)[mi]);
-    }
-    sMask[j] = m;
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_lane = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-  const uint32_t tS = t_lane;              // columns [0,128)
-  const uint32_t tO = t_lane + BN;         // columns [128,128+DP)
 
-  constexpr uint32_t kIdescS = make_idesc(kBf16, false, false, BM, BN);
-  constexpr uint32_t kIdescO = make_idesc(kBf16, false, true, BM, DP);
-
-  auto issue_s_mma = [&]() {
-    const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK);
-#pragma unroll
-    for (int kk = 0; kk < DP / 16; ++kk) {
-      const uint64_t ad = make_sdesc(qa + kk * 32, 16, 8 * RB, SWZ);
-      const uint64_t bd = make_sdesc(ka + kk * 32, 16, 8 * RB, SWZ);
-      mma_ss(tmem, ad, bd, kIdescS, kk > 0 ? 1u : 0u);
-    }
-    mma_commit(bar_s);
-  };
-  auto issue_o_mma = [&]() {
-    const uint32_t pa = smem_u32(sP), va = smem_u32(sV);
-#pragma unroll
-    for (int kk = 0; kk < BN / 16; ++kk) {
-      const uint64_t ad = make_sdesc(pa + (kk >> 2) * (BM * 128) + (kk & 3) * 32, 16, 1024, SWZ_128B);
-      const uint64_t bd = make_sdesc(va + kk * 16 * RB, 16, 8 * RB, SWZ);
-      mma_ss(tmem + BN, ad, bd, kIdescO, kk > 0 ? 1u : 0u);
-    }
-    mma_commit(bar_o);
-  };
-  // Pair-bias chunk c (0..3) of key tile jt -> this warpgroup's buffer.
-  auto issue_bias = [&](int jt, int c) {
-    mbar_expect_tx(bar_b + wg, L::kBiasChunk);
-    tma_load_4d(sB + wg * L::kBiasChunk, &tmB, bar_b + wg, jt * BN + c * 32, i0, h, b);
-  };
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_q, L::kTile);
-    tma_load_5d(sQ, &tmQ, bar_q, 0, i0, s, h, b);
-    mbar_expect_tx(bar_k, L::kTile);
-    tma_load_5d(sK, &tmK, bar_k, 0, 0, s, h, b);
-    mbar_expect_tx(bar_v, L::kTile);
-    tma_load_5d(sV, &tmV, bar_v, 0, 0, s, h, b);
-  }
-  if (has_bias && (tid & 127) == 0) issue_bias(0, wg * 2);
-  if (tid == 0) {
-    mbar_wait(bar_q, 0, abort_flag, a.status, DEV_TIMEOUT_TMA);
-    mbar_wait(bar_k, 0, abort_flag, a.status, DEV_TIMEOUT_TMA);
-    tc_fence_after();
-    issue_s_mma();
-  }
-
-  float m_run = -FLT_MAX, l_run = 0.f;
-  float acc[HALF_D];
-#pragma unroll
-  for (int d = 0; d < HALF_D; ++d) acc[d] = 0.f;
-  uint32_t bias_phase = 0;
-  const float scale = a.scale;
-
-  for (int jt = 0; jt < NT; ++jt) {
-    const uint32_t ph = jt & 1;
-    mbar_wait(bar_s, ph, abort_flag, a.status, DEV_TIMEOUT_MMA);
-    tc_fence_after();
-    if (tid == 0 && jt + 1 < NT) {  // S MMA is done with the K tile
-      mbar_expect_tx(bar_k, L::kTile);
-      tma_load_5d(sK, &tmK, bar_k, 0, (jt + 1) * BN, s, h, b);
-    }
-
-    // ---- scores of my 64 columns: x = scale*S + bias, then the mask
-    float x[64];
-    float mx = -FLT_MAX;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t sr[32];
-      tmem_ld32(tS + wg * 64 + c * 32, sr);
-      float bv[32];
-      if (has_bias) {
-        mbar_wait(bar_b + wg, bias_phase, abort_flag, a.status, DEV_TIMEOUT_TMA);
-        bias_phase ^= 1;
-        const uint8_t* brow = sB + wg * L::kBiasChunk + row * 128;
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          const float4 f = *reinterpret_cast<const float4*>(brow + ((q4 ^ (row & 7)) << 4));
-          bv[q4 * 4 + 0] = f.x; bv[q4 * 4 + 1] = f.y; bv[q4 * 4 + 2] = f.z; bv[q4 * 4 + 3] = f.w;
+  if (warp < 4) {
+    setmaxnreg_dec<40>();
+    if (warp == 0 && lane == 0) {
+      // =============================== TMA producer ===============================
+      uint32_t qn[2] = {0, 0}, gt = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const Item it = decode_item(item, NSP, NQT, a.H);
+        int srow[2];
+        srow[0] = min(2 * it.sp, a.S - 1);
+        srow[1] = min(2 * it.sp + 1, a.S - 1);
+        for (int w = 0; w < 2; ++w) {
+          const int st = qn[w] % QST;
+          mbar_wait(q_empty(w, st), ((qn[w] / QST) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+          mbar_expect_tx(q_full(w, st), C::kQ);
+          tma_load_5d(smem + C::offQ + (w * QST + st) * C::kQ, &tmQ, q_full(w, st), 0, it.qt * BM, srow[w], it.h, it.b);
+          ++qn[w];
         }
-        named_bar_sync(1 + wg, 128);  // the whole warpgroup has read the chunk
-        if ((tid & 127) == 0) {
-          if (c == 0) issue_bias(jt, wg * 2 + 1);
-          else if (jt + 1 < NT) issue_bias(jt + 1, wg * 2);
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) bv[e] = 0.f;
-      }
-      tmem_wait_ld();
-      const float* mrow = sMask + jt * BN + wg * 64 + c * 32;
-#pragma unroll
-      for (int e4 = 0; e4 < 8; ++e4) {
-        const float4 mk = *reinterpret_cast<const float4*>(mrow + e4 * 4);
-        const float mkv[4] = {mk.x, mk.y, mk.z, mk.w};
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int e = e4 * 4 + u;
-          float v = fmaf(__uint_as_float(sr[e]), scale, bv[e]);
-          v = (MASKMODE == MASK_MIN) ? fminf(v, mkv[u]) : (v + mkv[u]);
-          x[c * 32 + e] = v;
-          mx = fmaxf(mx, v);
+        for (int t = 0; t < T_TILES; ++t, ++gt) {
+          const int st = gt % NKV;
+          const uint32_t par = ((gt / NKV) & 1) ^ 1;
+          for (int w = 0; w < 2; ++w) {
+            mbar_wait(k_empty(w, st), par, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+            mbar_expect_tx(k_full(w, st), C::kKV);
+            tma_load_5d(smem + C::offK + (w * NKV + st) * C::kKV, &tmK, k_full(w, st), 0, t * BN, srow[w], it.h, it.b);
+          }
+          if (has_bias) {
+            const int bs = gt % BST;
+            mbar_wait(b_empty(bs), ((gt / BST) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+            mbar_expect_tx(b_full(bs), C::kBias);
+            uint8_t* dst = smem + C::offB + bs * C::kBias;
+            tma_load_4d(dst, &tmB, b_full(bs), t * BN, it.qt * BM, it.h, it.b);
+            tma_load_4d(dst + C::kBias / 2, &tmB, b_full(bs), t * BN + 32, it.qt * BM, it.h, it.b);
+          }
+          for (int w = 0; w < 2; ++w) {
+            mbar_wait(v_empty(w, st), par, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+            mbar_expect_tx(v_full(w, st), C::kKV);
+            tma_load_5d(smem + C::offV + (w * NKV + st) * C::kKV, &tmV, v_full(w, st), 0, t * BN, srow[w], it.h, it.b);
+          }
         }
       }
-    }
-    sPmax[wg * BM + row] = mx;
-    tc_fence_before();
-    __syncthreads();  // (1) all S reads done; partial row maxima visible
-    if (tid == 0 && jt + 1 < NT) {
-      mbar_wait(bar_k, (jt + 1) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
-      tc_fence_after();
-      issue_s_mma();  // next tile's scores overlap this tile's exponentials
-    }
-    const float m_new = fmaxf(m_run, fmaxf(sPmax[row], sPmax[BM + row]));
-    // A row whose keys are all dropped so far has every score at -FLT_MAX: its
-    // probabilities are uniform over the real keys (test.py:54-55 semantics).
-    const bool dead = (m_new == -FLT_MAX);
-    const float alpha = dead ? 1.f : ex2((m_run - m_new) * kLog2e);
-    const float nm2 = -m_new * kLog2e;
-    float lsum = 0.f;
-    uint8_t* prow = sP + wg * (BM * 128) + row * 128;
+    } else if (warp == 1 && lane == 0) {
+      // =============================== MMA issuer ===============================
+      constexpr uint32_t kIdescS = make_idesc(kBf16, false, false, BM, BN);
+      constexpr uint32_t kIdescO = make_idesc(kBf16, false, true, BM, DP);
+      uint32_t qn = 0, base = 0;  // items done, key tiles done (same for both warpgroups)
+      auto issue_s = [&](int w, uint32_t g) {  // g: running key-tile index of this warpgroup
+        const int st = g % NKV;
+        mbar_wait(k_full(w, st), (g / NKV) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        tc_fence_after();
+        const uint32_t qa = smem_u32(smem + C::offQ + (w * QST + (qn % QST)) * C::kQ);
+        const uint32_t ka = smem_u32(smem + C::offK + (w * NKV + st) * C::kKV);
+        const uint32_t d = tmem + w * C::tmemWg + (g & 1) * BN;
 #pragma unroll
-    for (int c8 = 0; c8 < 8; ++c8) {
-      float p[8];
+        for (int kk = 0; kk < DP / 16; ++kk)
+          mma_ss(d, make_sdesc(qa + kk * 32, 16, 8 * RB, SWZ), make_sdesc(ka + kk * 32, 16, 8 * RB, SWZ), kIdescS,
+                 kk > 0 ? 1u : 0u);
+        mma_commit(k_empty(w, st));
+        mma_commit(s_full(w, g & 1));
+      };
+      auto issue_pv = [&](int w, uint32_t g) {
+        const int st = g % NKV;
+        mbar_wait(p_full(w), g & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+        mbar_wait(v_full(w, st), (g / NKV) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        tc_fence_after();
+        const uint32_t pa = smem_u32(smem + C::offP + w * C::kP);
+        const uint32_t va = smem_u32(smem + C::offV + (w * NKV + st) * C::kKV);
+        const uint32_t d = tmem + w * C::tmemWg + 2 * BN + (g & 1) * DP;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int e = c8 * 8 + u;
-        if (!dead) p[u] = ex2(fmaf(x[e], kLog2e, nm2));
-        else p[u] = (jt * BN + wg * 64 + e < a.R) ? 1.f : 0.f;
-        lsum += p[u];
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_ss(d, make_sdesc(pa + kk * 32, 16, 1024, SWZ_128B), make_sdesc(va + kk * 16 * RB, 16, 8 * RB, SWZ),
+                 kIdescO, kk > 0 ? 1u : 0u);
+        mma_commit(v_empty(w, st));
+        mma_commit(o_full(w, g & 1));
+      };
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        for (int w = 0; w < 2; ++w)
+          mbar_wait(q_full(w, qn % QST), (qn / QST) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        for (int t = 0; t < 2 && t < T_TILES; ++t)
+          for (int w = 0; w < 2; ++w) issue_s(w, base + t);
+        for (int t = 0; t < T_TILES; ++t) {
+          for (int w = 0; w < 2; ++w) {
+            issue_pv(w, base + t);
+            if (t + 2 < T_TILES) issue_s(w, base + t + 2);  // S buffer (t&1) was read before P_t was signalled
+          }
+        }
+        for (int w = 0; w < 2; ++w) mma_commit(q_empty(w, qn % QST));
+        ++qn;
+        base += T_TILES;
       }
-      uint4 pk;
-      pk.x = Pack2<T>::pack(p[0], p[1]);
-      pk.y = Pack2<T>::pack(p[2], p[3]);
-      pk.z = Pack2<T>::pack(p[4], p[5]);
-      pk.w = Pack2<T>::pack(p[6], p[7]);
-      *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = pk;
     }
-    l_run = l_run * alpha + lsum;
-    m_run = m_new;
-    fence_async_shared();
-    __syncthreads();  // (2) P is complete in shared memory
-    if (tid == 0) {
-      mbar_wait(bar_v, ph, abort_flag, a.status, DEV_TIMEOUT_TMA);
-      tc_fence_after();
-      issue_o_mma();
-    }
+  } else {
+    // =============================== softmax warpgroups ===============================
+    setmaxnreg_inc<232>();
+    const int w = (warp >> 2) - 1;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t t_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + w * C::tmemWg;
+    float* mrow_base = sMask + w * r_pad;
+    uint8_t* prow = smem + C::offP + w * C::kP + row * 128;
+    const float scale = a.scale;
+    uint32_t g = 0;  // running key-tile index
+
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const Item it = decode_item(item, NSP, NQT, a.H);
+      const int s_raw = 2 * it.sp + w;
+      const bool active = s_raw < a.S;
+      const int s = active ? s_raw : a.S - 1;
+      const int i = it.qt * BM + row;
+
+      // residue-mask row of (b, s) as one float per key; keys beyond R are always excluded
+      named_bar_sync(1 + w, 128);  // previous item's readers are done
+      for (int j = row; j < r_pad; j += 128) {
+        float m;
+        if (j >= a.R) {
+          m = -FLT_MAX;
+        } else if (a.mask_kind == EVOATTN_MASK_NONE) {
+          m = (MASKMODE == MASK_MIN) ? FLT_MAX : 0.f;
+        } else {
+          const long long mi = (long long)it.b * a.smask.a + (long long)s * a.smask.b + (long long)j * a.smask.c;
+          if (MASKMODE == MASK_MIN) m = reinterpret_cast<const unsigned char*>(a.mask)[mi] ? FLT_MAX : -FLT_MAX;
+          else if (a.mask_kind == EVOATTN_MASK_ADD_F32) m = reinterpret_cast<const float*>(a.mask)[mi];
+          else m = to_float<T>(reinterpret_cast<const T*>(a.mask)[mi]);
+        }
+        mrow_base[j] = m;
+      }
+      named_bar_sync(1 + w, 128);
+
+      float m_run = -FLT_MAX, l_run = 0.f, alpha_pending = 1.f;
+      float acc[DP];
 #pragma unroll
-    for (int d = 0; d < HALF_D; ++d) acc[d] *= alpha;
-    mbar_wait(bar_o, ph, abort_flag, a.status, DEV_TIMEOUT_MMA);
-    tc_fence_after();
-    if (tid == 0 && jt + 1 < NT) {  // P V is done with the V tile
-      mbar_expect_tx(bar_v, L::kTile);
-      tma_load_5d(sV, &tmV, bar_v, 0, (jt + 1) * BN, s, h, b);
-    }
-    uint32_t orr[HALF_D];
-    tmem_ld<HALF_D>(tO + wg * HALF_D, orr);
-    tmem_wait_ld();
+      for (int d = 0; d < DP; ++d) acc[d] = 0.f;
+
+      for (int t = 0; t < T_TILES; ++t, ++g) {
+        mbar_wait(s_full(w, g & 1), (g >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
+        tc_fence_after();
+        if (has_bias) mbar_wait(b_full(g % BST), (g / BST) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        const uint8_t* bstage = smem + C::offB + (g % BST) * C::kBias + row * 128;
+        const float* mrow = mrow_base + t * BN;
+
+        float x[BN];
+        float mx = -FLT_MAX;
 #pragma unroll
-    for (int d = 0; d < HALF_D; ++d) acc[d] += __uint_as_float(orr[d]);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sr[32];
+          tmem_ld32(t_base + (g & 1) * BN + c * 32, sr);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4) {
+            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (has_bias) bv = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + ((q4 ^ (row & 7)) << 4));
+            const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + q4 * 4);
+            const float bvv[4] = {bv.x, bv.y, bv.z, bv.w};
+            const float mkv[4] = {mk.x, mk.y, mk.z, mk.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int e = c * 32 + q4 * 4 + u;
+              float v = fmaf(__uint_as_float(sr[q4 * 4 + u]), scale, bvv[u]);
+              v = (MASKMODE == MASK_MIN) ? fminf(v, mkv[u]) : (v + mkv[u]);
+              x[e] = v;
+              mx = fmaxf(mx, v);
+            }
+          }
+        }
+        if (has_bias) mbar_arrive(b_empty(g % BST));
+
+        const float m_new = fmaxf(m_run, mx);
+        const float alpha = ex2((m_run - m_new) * kLog2e);
+        float lsum = 0.f;
+        uint32_t pk[BN / 2];
+        if (m_new != -FLT_MAX) {
+          const float nm2 = -m_new * kLog2e;
+#pragma unroll
+          for (int e = 0; e < BN; e += 2) {
+            const float p0 = ex2(fmaf(x[e], kLog2e, nm2));
+            const float p1 = ex2(fmaf(x[e + 1], kLog2e, nm2));
+            lsum += p0 + p1;
+            pk[e / 2] = Pack2<T>::pack(p0, p1);
+          }
+        } else {
+          // every key seen so far was dropped: the scores are all -FLT_MAX and the softmax is
+          // uniform over the real keys (test.py:54-55 semantics)
+#pragma unroll
+          for (int e = 0; e < BN; e += 2) {
+            const float p0 = (t * BN + e < a.R) ? 1.f : 0.f;
+            const float p1 = (t * BN + e + 1 < a.R) ? 1.f : 0.f;
+            lsum += p0 + p1;
+            pk[e / 2] = Pack2<T>::pack(p0, p1);
+          }
+        }
+        l_run = l_run * alpha + lsum;
+        m_run = m_new;
+
+        // fold the previous tile's P V into the accumulator (its MMA ran while we did the exps)
+        if (t > 0) {
+          mbar_wait(o_full(w, (g - 1) & 1), ((g - 1) >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
+          tc_fence_after();
+          uint32_t orr[DP];
+          tmem_ld<(DP >= 32 ? 32 : 16)>(t_base + 2 * BN + ((g - 1) & 1) * DP, *reinterpret_cast<uint32_t(*)[DP >= 32 ? 32 : 16]>(&orr[0]));
+          if constexpr (DP == 64)
+            tmem_ld32(t_base + 2 * BN + ((g - 1) & 1) * DP + 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[32]));
+          tmem_wait_ld();
+#pragma unroll
+          for (int d = 0; d < DP; ++d) acc[d] = fmaf(acc[d], alpha_pending, __uint_as_float(orr[d]));
+        }
+        alpha_pending = alpha;
+
+        // P_n -> shared memory (K-major, 128B swizzle); its previous reader P V_{n-1} has completed
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+          uint4 v4;
+          v4.x = pk[c8 * 4 + 0]; v4.y = pk[c8 * 4 + 1]; v4.z = pk[c8 * 4 + 2]; v4.w = pk[c8 * 4 + 3];
+          *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = v4;
+        }
+        fence_async_shared();
+        tc_fence_before();
+        mbar_arrive(p_full(w));
+      }
+      // last tile's P V
+      {
+        mbar_wait(o_full(w, (g - 1) & 1), ((g - 1) >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
+        tc_fence_after();
+        uint32_t orr[DP];
+        tmem_ld<(DP >= 32 ? 32 : 16)>(t_base + 2 * BN + ((g - 1) & 1) * DP, *reinterpret_cast<uint32_t(*)[DP >= 32 ? 32 : 16]>(&orr[0]));
+        if constexpr (DP == 64)
+          tmem_ld32(t_base + 2 * BN + ((g - 1) & 1) * DP + 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[32]));
+        tmem_wait_ld();
+#pragma unroll
+        for (int d = 0; d < DP; ++d) acc[d] = fmaf(acc[d], alpha_pending, __uint_as_float(orr[d]));
+      }
+      if (active && i < a.R) {
+        const float inv = 1.f / l_run;
+        T* orow = reinterpret_cast<T*>(a.o) + off4(a.so, it.b, it.h, s, i);
+#pragma unroll
+        for (int d8 = 0; d8 < DP / 8; ++d8) {
+          if (d8 * 8 < a.D) {
+            uint4 v4;
+            v4.x = Pack2<T>::pack(acc[d8 * 8 + 0] * inv, acc[d8 * 8 + 1] * inv);
+            v4.y = Pack2<T>::pack(acc[d8 * 8 + 2] * inv, acc[d8 * 8 + 3] * inv);
+            v4.z = Pack2<T>::pack(acc[d8 * 8 + 4] * inv, acc[d8 * 8 + 5] * inv);
+            v4.w = Pack2<T>::pack(acc[d8 * 8 + 6] * inv, acc[d8 * 8 + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + d8 * 8) = v4;
+          }
+        }
+        const long long li = (((long long)it.b * a.H + it.h) * a.S + s) * a.R + i;
+        a.lse[li] = (m_run == -FLT_MAX) ? -FLT_MAX : (m_run + logf(l_run));
+      }
+    }
   }
 
-  // ---- epilogue: combine the two column halves' row sums, normalise, store
-  sPsum[wg * BM + row] = l_run;
-  tc_fence_before();
-  __syncthreads();
-  const float l_tot = sPsum[row] + sPsum[BM + row];
-  const float inv = 1.f / l_tot;
-  const int i = i0 + row;
-  if (i < a.R) {
-    T* orow = reinterpret_cast<T*>(a.o) + off4(a.so, b, h, s, i) + wg * HALF_D;
-#pragma unroll
-    for (int d8 = 0; d8 < HALF_D / 8; ++d8) {
-      if (wg * HALF_D + d8 * 8 < a.D) {
-        uint4 pk;
-        pk.x = Pack2<T>::pack(acc[d8 * 8 + 0] * inv, acc[d8 * 8 + 1] * inv);
-        pk.y = Pack2<T>::pack(acc[d8 * 8 + 2] * inv, acc[d8 * 8 + 3] * inv);
-        pk.z = Pack2<T>::pack(acc[d8 * 8 + 4] * inv, acc[d8 * 8 + 5] * inv);
-        pk.w = Pack2<T>::pack(acc[d8 * 8 + 6] * inv, acc[d8 * 8 + 7] * inv);
-        *reinterpret_cast<uint4*>(orow + d8 * 8) = pk;
-      }
-    }
-    if (wg == 0) {
-      const long long li = (((long long)b * a.H + h) * a.S + s) * a.R + i;
-      a.lse[li] = (m_run == -FLT_MAX) ? -FLT_MAX : (m_run + logf(l_tot));
-    }
-  }
   if (*abort_flag) {
     // give copies that may still be in flight time to land before the CTA retires
     const long long t0 = clock64();
     while (clock64() - t0 < 200000) {}
   }
+  tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
+int g_num_sms = 0;
+
 template <class T, int DP>
 int launch_t(const Args& a, cudaStream_t st, int* launches) {
-  using L = FwdSmem<DP>;
+  using C = Cfg<DP>;
   CUtensorMap tq, tk, tv, tb;
   if (!make_qkv_map(&tq, a.q, a.sq, a.B, a.H, a.S, a.R, a.D, DP, BM)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tk, a.k, a.sk, a.B, a.H, a.S, a.R, a.D, DP, BN)) return EVOATTN_ERR_CUDA;
@@ -356,14 +436,22 @@ int launch_t(const Args& a, cudaStream_t st, int* launches) {
   } else {
     tb = tq;
   }
-  const int NT = (a.R + BN - 1) / BN;
-  const size_t smem = L::bytes(NT * BN);
-  const long long ctas = (long long)a.B * a.H * a.S * ((a.R + BM - 1) / BM);
+  if (g_num_sms == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      return EVOATTN_ERR_CUDA;
+    g_num_sms = n;
+  }
+  const int T_TILES = (a.R + BN - 1) / BN;
+  const size_t smem = C::bytes(T_TILES * BN);
+  const long long items = (long long)a.B * a.H * ((a.R + BM - 1) / BM) * ((a.S + 1) / 2);
+  const int grid = (int)(items < g_num_sms ? items : g_num_sms);
   const bool add = a.mask_kind == EVOATTN_MASK_ADD_F32 || a.mask_kind == EVOATTN_MASK_ADD_SAME;
   auto kern = add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD> : evo_fwd_sm100_kernel<T, DP, MASK_MIN>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return EVOATTN_ERR_CUDA;
-  kern<<<(unsigned)ctas, kThreads, smem, st>>>(a, tq, tk, tv, tb);
+  kern<<<grid, kThreads, smem, st>>>(a, (int)items, tq, tk, tv, tb);
   *launches += 1;
   return cudaGetLastError() == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
 }
@@ -380,7 +468,7 @@ int launch_d(const Args& a, cudaStream_t st, int* launches) {
 bool sm100_fwd_supported(int dtype, const Args& a) {
   if (dtype != EVOATTN_BF16 && dtype != EVOATTN_FP16) return false;
   if (a.D % 8 != 0 || a.D > 64) return false;
-  if (a.R > 8192) return false;  // the mask row is staged in shared memory
+  if (a.R > 2048) return false;  // two mask rows are staged in shared memory
   if (a.bias) {
     if ((reinterpret_cast<uintptr_t>(a.bias) & 15) != 0) return false;
     if ((a.sbias.a * 4) % 16 || (a.sbias.b * 4) % 16 || (a.sbias.c * 4) % 16) return false;
