@@ -7,7 +7,8 @@
 //
 // Persistent, warp-specialised kernel, one CTA per SM, 384 threads:
 //   warp 0      TMA producer: Q tiles, K/V tiles (64 keys each) and pair-bias tiles
-//   warp 1      issues every tcgen05.mma
+//   warp 1, 2   issue the tcgen05.mma of warpgroup A, B
+//   warp 3      stages the residue-mask rows of the next item in shared memory
 //   warps 4-7   softmax warpgroup A        warps 8-11   softmax warpgroup B
 // A work item is one 128-row query tile of TWO consecutive MSA rows s of one (b,h):
 // warpgroup A takes row 2p, B takes row 2p+1.  Both rows use the same pair-bias tile, so
@@ -16,8 +17,9 @@
 // maximum and sum need no exchange between threads.
 //
 // Per warpgroup and key tile n:  S_n = Q K_n^T lands in TMEM (double buffered); the
-// warpgroup turns it into P_n (rounded to the storage type as evoformer.py:84 does) in
-// shared memory; P_n V_n lands in a second TMEM double buffer and is folded into the
+// warpgroup turns it into P_n (rounded to the storage type as evoformer.py:84 does) and
+// writes it back over S_n in TMEM, from where it feeds the P V MMA as the A operand;
+// P_n V_n lands in a second TMEM double buffer and is folded into the
 // fp32 output accumulator in registers one tile later, scaled by the softmax correction
 // of that tile.  The MMA warp runs S_{n+1} while the warpgroup is busy with tile n.
 #include <type_traits>
@@ -56,9 +58,9 @@ struct Cfg {
   static constexpr int offP = offV + 2 * NKV * kKV;
   static constexpr int offB = offP + 2 * kP;
   static constexpr int offMask = offB + BST * kBias;
-  static constexpr int kNumBars = 2 * (2 * QST + 4 * NKV + 2 + 1 + 2) + 2 * BST;
+  static constexpr int kNumBars = 2 * (2 * QST + 4 * NKV + 2 + 1 + 2 + 4) + 2 * BST;
   static size_t bytes(int r_pad) {
-    return (size_t)offMask + (size_t)2 * r_pad * 4 + kNumBars * 8 + 64 + 1024;
+    return (size_t)offMask + (size_t)4 * r_pad * 4 + kNumBars * 8 + 64 + 1024;
   }
   // TMEM columns of warpgroup w: S double buffer, then PV double buffer
   static constexpr int tmemWg = 2 * BN + 2 * DP;
@@ -111,10 +113,10 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int T_TILES = (a.R + BN - 1) / BN;
   const int r_pad = T_TILES * BN;
-  float* sMask = reinterpret_cast<float*>(smem + C::offMask);  // [2][r_pad]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sMask + 2 * r_pad);
+  float* sMask = reinterpret_cast<float*>(smem + C::offMask);  // [warpgroup][stage][r_pad]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sMask + 4 * r_pad);
   // barrier layout: per warpgroup w a block of PER, then the shared bias barriers
-  constexpr int PER = 2 * QST + 4 * NKV + 2 + 1 + 2;
+  constexpr int PER = 2 * QST + 4 * NKV + 2 + 1 + 2 + 4;
   auto q_full = [&](int w, int st) { return bars + w * PER + st; };
   auto q_empty = [&](int w, int st) { return bars + w * PER + QST + st; };
   auto k_full = [&](int w, int st) { return bars + w * PER + 2 * QST + st; };
@@ -124,6 +126,8 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
   auto s_full = [&](int w, int i) { return bars + w * PER + 2 * QST + 4 * NKV + i; };
   auto p_full = [&](int w) { return bars + w * PER + 2 * QST + 4 * NKV + 2; };
   auto o_full = [&](int w, int i) { return bars + w * PER + 2 * QST + 4 * NKV + 3 + i; };
+  auto m_full = [&](int w, int st) { return bars + w * PER + 2 * QST + 4 * NKV + 5 + st; };
+  auto m_empty = [&](int w, int st) { return bars + w * PER + 2 * QST + 4 * NKV + 7 + st; };
   auto b_full = [&](int st) { return bars + 2 * PER + st; };
   auto b_empty = [&](int st) { return bars + 2 * PER + BST + st; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
@@ -149,6 +153,7 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
       mbar_init(s_full(w, 0), 1); mbar_init(s_full(w, 1), 1);
       mbar_init(p_full(w), 128);
       mbar_init(o_full(w, 0), 1); mbar_init(o_full(w, 1), 1);
+      for (int st = 0; st < 2; ++st) { mbar_init(m_full(w, st), 32); mbar_init(m_empty(w, st), 128); }
     }
     for (int st = 0; st < BST; ++st) { mbar_init(b_full(st), 1); mbar_init(b_empty(st), 256); }
     fence_mbar_init();
@@ -204,54 +209,85 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
           }
         }
       }
-    } else if (warp == 1 && lane == 0) {
-      // =============================== MMA issuer ===============================
+    } else if ((warp == 1 || warp == 2) && lane == 0) {
+      // =============================== MMA issuer of warpgroup w ===============================
+      const int w = warp - 1;
       constexpr uint32_t kIdescS = make_idesc(kBf16, false, false, BM, BN);
       constexpr uint32_t kIdescO = make_idesc(kBf16, false, true, BM, DP);
-      uint32_t qn = 0, base = 0;  // items done, key tiles done (same for both warpgroups)
-      auto issue_s = [&](int w, uint32_t g) {  // g: running key-tile index of this warpgroup
+      // Descriptor halves that never change: the high word holds the stride offset, version and
+      // swizzle; the low word is (address >> 4) plus the leading-offset field.
+      constexpr uint32_t kHiOp = static_cast<uint32_t>(make_sdesc_const(16, 8 * RB, SWZ) >> 32);
+      constexpr uint32_t kLoLbo = static_cast<uint32_t>(make_sdesc_const(16, 0, 0) & 0xffffffffu);
+      const uint32_t q_lo0 = (smem_u32(smem + C::offQ + w * QST * C::kQ) >> 4) | kLoLbo;
+      const uint32_t k_lo0 = (smem_u32(smem + C::offK + w * NKV * C::kKV) >> 4) | kLoLbo;
+      const uint32_t v_lo0 = (smem_u32(smem + C::offV + w * NKV * C::kKV) >> 4) | kLoLbo;
+      const uint32_t tS = tmem + w * C::tmemWg, tO = tS + 2 * BN;
+      uint32_t qn = 0, base = 0;  // items done, key tiles done
+      auto issue_s = [&](uint32_t g) {  // g: running key-tile index
         const int st = g % NKV;
         mbar_wait(k_full(w, st), (g / NKV) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
         tc_fence_after();
-        const uint32_t qa = smem_u32(smem + C::offQ + (w * QST + (qn % QST)) * C::kQ);
-        const uint32_t ka = smem_u32(smem + C::offK + (w * NKV + st) * C::kKV);
-        const uint32_t d = tmem + w * C::tmemWg + (g & 1) * BN;
+        const uint32_t qa = q_lo0 + (qn % QST) * (C::kQ >> 4);
+        const uint32_t ka = k_lo0 + st * (C::kKV >> 4);
 #pragma unroll
         for (int kk = 0; kk < DP / 16; ++kk)
-          mma_ss(d, make_sdesc(qa + kk * 32, 16, 8 * RB, SWZ), make_sdesc(ka + kk * 32, 16, 8 * RB, SWZ), kIdescS,
+          mma_ss(tS + (g & 1) * BN, pack_desc(qa + kk * 2, kHiOp), pack_desc(ka + kk * 2, kHiOp), kIdescS,
                  kk > 0 ? 1u : 0u);
         mma_commit(k_empty(w, st));
         mma_commit(s_full(w, g & 1));
       };
-      auto issue_pv = [&](int w, uint32_t g) {
+      auto issue_pv = [&](uint32_t g) {
         const int st = g % NKV;
-        mbar_wait(p_full(w), g & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
         mbar_wait(v_full(w, st), (g / NKV) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        mbar_wait(p_full(w), g & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
         tc_fence_after();
-        const uint32_t pa = smem_u32(smem + C::offP + w * C::kP);
-        const uint32_t va = smem_u32(smem + C::offV + (w * NKV + st) * C::kKV);
-        const uint32_t d = tmem + w * C::tmemWg + 2 * BN + (g & 1) * DP;
+        const uint32_t va = v_lo0 + st * (C::kKV >> 4);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          mma_ss(d, make_sdesc(pa + kk * 32, 16, 1024, SWZ_128B), make_sdesc(va + kk * 16 * RB, 16, 8 * RB, SWZ),
-                 kIdescO, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < BN / 16; ++kk)  // 16 keys = 8 packed columns of P per step
+          mma_ts(tO + (g & 1) * DP, tS + (g & 1) * BN + kk * 8, pack_desc(va + kk * RB, kHiOp), kIdescO,
+                 kk > 0 ? 1u : 0u);
         mma_commit(v_empty(w, st));
         mma_commit(o_full(w, g & 1));
       };
       for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        for (int w = 0; w < 2; ++w)
-          mbar_wait(q_full(w, qn % QST), (qn / QST) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
-        for (int t = 0; t < 2 && t < T_TILES; ++t)
-          for (int w = 0; w < 2; ++w) issue_s(w, base + t);
+        mbar_wait(q_full(w, qn % QST), (qn / QST) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        for (int t = 0; t < 2 && t < T_TILES; ++t) issue_s(base + t);
         for (int t = 0; t < T_TILES; ++t) {
-          for (int w = 0; w < 2; ++w) {
-            issue_pv(w, base + t);
-            if (t + 2 < T_TILES) issue_s(w, base + t + 2);  // S buffer (t&1) was read before P_t was signalled
-          }
+          issue_pv(base + t);
+          if (t + 2 < T_TILES) issue_s(base + t + 2);  // S buffer (t&1) was read before P_t was signalled
         }
-        for (int w = 0; w < 2; ++w) mma_commit(q_empty(w, qn % QST));
+        mma_commit(q_empty(w, qn % QST));
         ++qn;
         base += T_TILES;
+      }
+    } else if (warp == 3) {
+      // =============================== residue-mask stager ===============================
+      // One float per key for each warpgroup's MSA row, one item ahead of the softmax warps.
+      // Keys beyond R are always excluded.
+      uint32_t n = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n) {
+        const Item it = decode_item(item, NSP, NQT, a.H);
+        const int st = n & 1;
+        for (int w = 0; w < 2; ++w) {
+          const int s = min(2 * it.sp + w, a.S - 1);
+          mbar_wait(m_empty(w, st), ((n >> 1) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+          float* dst = sMask + (w * 2 + st) * r_pad;
+          for (int j = lane; j < r_pad; j += 32) {
+            float m;
+            if (j >= a.R) {
+              m = -FLT_MAX;
+            } else if (a.mask_kind == EVOATTN_MASK_NONE) {
+              m = (MASKMODE == MASK_MIN) ? FLT_MAX : 0.f;
+            } else {
+              const long long mi = (long long)it.b * a.smask.a + (long long)s * a.smask.b + (long long)j * a.smask.c;
+              if (MASKMODE == MASK_MIN) m = reinterpret_cast<const unsigned char*>(a.mask)[mi] ? FLT_MAX : -FLT_MAX;
+              else if (a.mask_kind == EVOATTN_MASK_ADD_F32) m = reinterpret_cast<const float*>(a.mask)[mi];
+              else m = to_float<T>(reinterpret_cast<const T*>(a.mask)[mi]);
+            }
+            dst[j] = m;
+          }
+          mbar_arrive(m_full(w, st));
+        }
       }
     }
   } else {
@@ -260,35 +296,25 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
     const int w = (warp >> 2) - 1;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t t_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + w * C::tmemWg;
-    float* mrow_base = sMask + w * r_pad;
-    uint8_t* prow = smem + C::offP + w * C::kP + row * 128;
     const float scale = a.scale;
-    uint32_t g = 0;  // running key-tile index
+    uint32_t g = 0, n_item = 0;  // running key-tile and item index
+    // The two warpgroups take turns in the exponential phase (named barriers 1 and 2 pass a
+    // token back and forth): while one keeps the MUFU busy, the other runs its load / bias /
+    // mask / max phase on the FMA, ALU and shared-memory pipes instead of both queueing on
+    // the same unit.
+    if (w == 1) named_bar_arrive(1, 256);
 
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
       const Item it = decode_item(item, NSP, NQT, a.H);
       const int s_raw = 2 * it.sp + w;
       const bool active = s_raw < a.S;
       const int s = active ? s_raw : a.S - 1;
       const int i = it.qt * BM + row;
 
-      // residue-mask row of (b, s) as one float per key; keys beyond R are always excluded
-      named_bar_sync(1 + w, 128);  // previous item's readers are done
-      for (int j = row; j < r_pad; j += 128) {
-        float m;
-        if (j >= a.R) {
-          m = -FLT_MAX;
-        } else if (a.mask_kind == EVOATTN_MASK_NONE) {
-          m = (MASKMODE == MASK_MIN) ? FLT_MAX : 0.f;
-        } else {
-          const long long mi = (long long)it.b * a.smask.a + (long long)s * a.smask.b + (long long)j * a.smask.c;
-          if (MASKMODE == MASK_MIN) m = reinterpret_cast<const unsigned char*>(a.mask)[mi] ? FLT_MAX : -FLT_MAX;
-          else if (a.mask_kind == EVOATTN_MASK_ADD_F32) m = reinterpret_cast<const float*>(a.mask)[mi];
-          else m = to_float<T>(reinterpret_cast<const T*>(a.mask)[mi]);
-        }
-        mrow_base[j] = m;
-      }
-      named_bar_sync(1 + w, 128);
+      // residue-mask row of (b, s), staged by warp 3
+      const uint32_t mst = n_item & 1;
+      mbar_wait(m_full(w, mst), (n_item >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+      const float* mrow_base = sMask + (w * 2 + mst) * r_pad;
 
       float m_run = -FLT_MAX, l_run = 0.f, alpha_pending = 1.f;
       float acc[DP];
@@ -302,45 +328,66 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         const uint8_t* bstage = smem + C::offB + (g % BST) * C::kBias + row * 128;
         const float* mrow = mrow_base + t * BN;
 
+        // scores of my row: x = scale*S + bias, then the mask.  Written in groups of eight
+        // independent elements (loads, FMAs, mins, then eight separate max chains) so that the
+        // in-order issue never waits on the previous instruction's result.
         float x[BN];
-        float mx = -FLT_MAX;
+        float mx8[8];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t sr[32];
-          tmem_ld32(t_base + (g & 1) * BN + c * 32, sr);
-          tmem_wait_ld();
+        for (int u = 0; u < 8; ++u) mx8[u] = -FLT_MAX;
+        uint32_t sr[BN];
+        tmem_ld32(t_base + (g & 1) * BN, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+        tmem_ld32(t_base + (g & 1) * BN + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+        tmem_wait_ld();
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4) {
-            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (has_bias) bv = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + ((q4 ^ (row & 7)) << 4));
-            const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + q4 * 4);
-            const float bvv[4] = {bv.x, bv.y, bv.z, bv.w};
-            const float mkv[4] = {mk.x, mk.y, mk.z, mk.w};
+        for (int g8 = 0; g8 < BN / 8; ++g8) {
+          const int c = g8 >> 2, q4 = (g8 & 3) * 2;
+          float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+          if (has_bias) {
+            b0 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + ((q4 ^ (row & 7)) << 4));
+            b1 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + (((q4 + 1) ^ (row & 7)) << 4));
+          }
+          const float4 k0 = *reinterpret_cast<const float4*>(mrow + g8 * 8);
+          const float4 k1 = *reinterpret_cast<const float4*>(mrow + g8 * 8 + 4);
+          const float bvv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+          const float mkv[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+          float v[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int e = c * 32 + q4 * 4 + u;
-              float v = fmaf(__uint_as_float(sr[q4 * 4 + u]), scale, bvv[u]);
-              v = (MASKMODE == MASK_MIN) ? fminf(v, mkv[u]) : (v + mkv[u]);
-              x[e] = v;
-              mx = fmaxf(mx, v);
-            }
+          for (int u = 0; u < 8; ++u) v[u] = fmaf(__uint_as_float(sr[g8 * 8 + u]), scale, bvv[u]);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = (MASKMODE == MASK_MIN) ? fminf(v[u], mkv[u]) : (v[u] + mkv[u]);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            x[g8 * 8 + u] = v[u];
+            mx8[u] = fmaxf(mx8[u], v[u]);
           }
         }
+        const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                               fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
         if (has_bias) mbar_arrive(b_empty(g % BST));
 
         const float m_new = fmaxf(m_run, mx);
         const float alpha = ex2((m_run - m_new) * kLog2e);
         float lsum = 0.f;
         uint32_t pk[BN / 2];
+        named_bar_sync(1 + w, 256);  // my turn on the exponential unit
         if (m_new != -FLT_MAX) {
           const float nm2 = -m_new * kLog2e;
+          float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int e = 0; e < BN; e += 2) {
-            const float p0 = ex2(fmaf(x[e], kLog2e, nm2));
-            const float p1 = ex2(fmaf(x[e + 1], kLog2e, nm2));
-            lsum += p0 + p1;
-            pk[e / 2] = Pack2<T>::pack(p0, p1);
+          for (int g8 = 0; g8 < BN / 8; ++g8) {
+            float y[8], p[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) y[u] = fmaf(x[g8 * 8 + u], kLog2e, nm2);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) p[u] = ex2(y[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              ls4[u] += p[2 * u] + p[2 * u + 1];
+              pk[g8 * 4 + u] = Pack2<T>::pack(p[2 * u], p[2 * u + 1]);
+            }
           }
+          lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
         } else {
           // every key seen so far was dropped: the scores are all -FLT_MAX and the softmax is
           // uniform over the real keys (test.py:54-55 semantics)
@@ -352,6 +399,7 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
             pk[e / 2] = Pack2<T>::pack(p0, p1);
           }
         }
+        named_bar_arrive(2 - w, 256);  // hand the turn to the other warpgroup
         l_run = l_run * alpha + lsum;
         m_run = m_new;
 
@@ -369,14 +417,11 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         }
         alpha_pending = alpha;
 
-        // P_n -> shared memory (K-major, 128B swizzle); its previous reader P V_{n-1} has completed
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          uint4 v4;
-          v4.x = pk[c8 * 4 + 0]; v4.y = pk[c8 * 4 + 1]; v4.z = pk[c8 * 4 + 2]; v4.w = pk[c8 * 4 + 3];
-          *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = v4;
-        }
-        fence_async_shared();
+        // P_n -> TMEM, packed two 16-bit values per column, over the first half of the S_n
+        // columns this thread has just consumed (lane = row, column j = keys 2j, 2j+1): the
+        // A operand of P V comes straight from tensor memory.
+        tmem_st32(t_base + (g & 1) * BN, pk);
+        tmem_wait_st();
         tc_fence_before();
         mbar_arrive(p_full(w));
       }
@@ -409,7 +454,9 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         const long long li = (((long long)it.b * a.H + it.h) * a.S + s) * a.R + i;
         a.lse[li] = (m_run == -FLT_MAX) ? -FLT_MAX : (m_run + logf(l_run));
       }
+      mbar_arrive(m_empty(w, mst));
     }
+    if (w == 0) named_bar_sync(1, 256);  // consume the last token so no arrival is left pending
   }
 
   if (*abort_flag) {

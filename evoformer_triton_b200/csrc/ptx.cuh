@@ -145,6 +145,16 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr, uint32_t lbo_byte
   return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
          (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (static_cast<uint64_t>(swz) << 61);
 }
+// The same encoding without the start address, usable in constant expressions, and the
+// assembly of a descriptor from a precomputed low word ((address >> 4) | leading-offset field)
+// and high word.
+__host__ __device__ constexpr uint64_t make_sdesc_const(uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swz) {
+  return (static_cast<uint64_t>(lbo_bytes >> 4) << 16) | (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) |
+         (static_cast<uint64_t>(swz) << 61);
+}
+__device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
+  return static_cast<uint64_t>(lo) | (static_cast<uint64_t>(hi) << 32);
+}
 __host__ __device__ constexpr uint32_t swizzle_code_for_row_bytes(int row_bytes) {
   return row_bytes == 128 ? SWZ_128B : (row_bytes == 64 ? SWZ_64B : SWZ_32B);
 }
@@ -216,6 +226,11 @@ __device__ __forceinline__ float ex2(float x) {
 // Named barrier among `nthreads` threads (ids 1..15; id 0 is __syncthreads).
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Non-blocking arrival on a named barrier that other threads wait on with named_bar_sync.
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 }  // namespace ptx
