@@ -16,8 +16,9 @@ PATH_NONE, PATH_GENERIC, PATH_TCGEN05 = 0, 1, 2
 
 SYMBOLS = (
     "evoattn_abi_version", "evoattn_strerror", "evoattn_fwd", "evoattn_bwd_workspace_bytes",
-    "evoattn_bwd", "evoattn_last_path", "evoattn_last_launch_count",
+    "evoattn_bwd", "evoattn_bwd_static_scratch", "evoattn_last_path", "evoattn_last_launch_count",
 )
+STATIC_SCRATCH_BYTES = 64 << 20
 
 
 class FwdParams(C.Structure):
@@ -75,6 +76,8 @@ def load() -> C.CDLL:
         lib.evoattn_bwd_workspace_bytes.argtypes = [C.POINTER(BwdParams)]
         lib.evoattn_bwd.restype = C.c_int
         lib.evoattn_bwd.argtypes = [C.POINTER(BwdParams), C.c_void_p]
+        lib.evoattn_bwd_static_scratch.restype = C.c_int
+        lib.evoattn_bwd_static_scratch.argtypes = [C.POINTER(BwdParams), C.c_void_p]
         lib.evoattn_last_path.restype = C.c_int
         lib.evoattn_last_launch_count.restype = C.c_int
         if lib.evoattn_abi_version() != ABI_VERSION:

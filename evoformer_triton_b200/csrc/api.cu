@@ -1,6 +1,8 @@
 // extern "C" surface of libevoattn.so: argument validation, dispatch, launches.
 #include <string.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "launch.h"
 
@@ -99,6 +101,29 @@ bool use_sm100_bwd(const evoattn_bwd_params* p, const evo::Args& a) {
   return evo::sm100_bwd_supported(p->fwd.dtype, a);
 }
 
+// Scratch of evoattn_bwd_static_scratch(): part of the library image, so every GPU that loads
+// the library holds it until the process exits.  In host code this name is only a stand-in
+// for the symbol, never a device address: the address is looked up per device below.
+static __device__ __align__(256) unsigned char g_static_scratch[EVOATTN_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the static scratch on the current device; looked up once per device.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return EVOATTN_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_addr[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return EVOATTN_ERR_CUDA;
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return EVOATTN_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -164,6 +189,31 @@ int evoattn_bwd(const evoattn_bwd_params* p, void* cuda_stream) {
   }
   g_last_path = EVOATTN_PATH_GENERIC;
   a.delta = reinterpret_cast<float*>(p->workspace);
+  return evo::launch_generic_bwd(p->fwd.dtype, a, st, &g_last_launches) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+}
+
+int evoattn_bwd_static_scratch(const evoattn_bwd_params* p, void* cuda_stream) {
+  g_last_path = EVOATTN_PATH_NONE;
+  g_last_launches = 0;
+  int rc = validate_bwd(p);
+  if (rc) return rc;
+  evo::Args a;
+  fill_bwd_args(p, &a);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  const bool fast = use_sm100_bwd(p, a);
+  const size_t need = fast ? evo::sm100_bwd_workspace_bytes(p->fwd.dtype, a) : generic_bwd_workspace(a);
+  if (need > EVOATTN_STATIC_SCRATCH_BYTES) return EVOATTN_ERR_WORKSPACE;
+  // Looking the symbol up also makes the device's primary context current on this thread,
+  // which the tensor-map encoder needs; nothing here allocates.
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  if (fast) {
+    g_last_path = EVOATTN_PATH_TCGEN05;
+    return evo::launch_sm100_bwd(p->fwd.dtype, a, scratch, EVOATTN_STATIC_SCRATCH_BYTES, st, &g_last_launches);
+  }
+  g_last_path = EVOATTN_PATH_GENERIC;
+  a.delta = reinterpret_cast<float*>(scratch);
   return evo::launch_generic_bwd(p->fwd.dtype, a, st, &g_last_launches) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
 }
 

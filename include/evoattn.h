@@ -3,7 +3,8 @@
  * flash attention, forward and backward) for NVIDIA B200 (sm_100a).
  *
  * Plain C, plain pointers and sizes.  The library owns no memory: every input,
- * output and scratch buffer is device memory allocated by the caller.  All work is
+ * output and scratch buffer is device memory allocated by the caller (the one exception
+ * is the fixed scratch array of evoattn_bwd_static_scratch, see there).  All work is
  * enqueued on the CUDA stream handed in (a cudaStream_t passed as void*); nothing
  * synchronises, nothing is freed, no pointer is kept after a call returns.
  *
@@ -121,6 +122,28 @@ size_t evoattn_bwd_workspace_bytes(const evoattn_bwd_params* p);
  * (evoformer.py:741-862: _attn_bwd_preprocess :299-326, _attn_bwd_dk_dv :479-630,
  * _attn_bwd_dq :329-476). */
 int evoattn_bwd(const evoattn_bwd_params* p, void* cuda_stream);
+
+/* Backward pass for callers that cannot hand the library a scratch buffer.  It has no
+ * counterpart in the reference.
+ *
+ * Some hosts of this library may not allocate device memory at the moment they need a
+ * backward pass: a runtime whose memory pool is fixed when the process starts, a plugin that
+ * runs inside someone else's allocator-free region, a serving loop with a frozen memory plan.
+ * For them this entry point is evoattn_bwd() with the scratch taken from a fixed array that
+ * is part of the library image (EVOATTN_STATIC_SCRATCH_BYTES of device memory on every GPU
+ * that loads the library, held until the process exits).  `workspace` and `workspace_bytes`
+ * in the parameters are ignored; inputs and outputs are still the caller's.
+ *
+ *  - A request that needs more than EVOATTN_STATIC_SCRATCH_BYTES of scratch (see
+ *    evoattn_bwd_workspace_bytes) returns EVOATTN_ERR_WORKSPACE and launches nothing.
+ *  - The function calls no cudaMalloc, cudaFree or any other allocating routine.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call before you start capturing a stream.
+ *  - All calls share the one array.  Whatever has to start from zero is cleared on the stream
+ *    by every call, but two calls that overlap on the GPU (different streams, no ordering)
+ *    race on it: keep calls on one device ordered. */
+#define EVOATTN_STATIC_SCRATCH_BYTES (64u << 20)
+int evoattn_bwd_static_scratch(const evoattn_bwd_params* p, void* cuda_stream);
 
 /* EVOATTN_PATH_* of the most recent forward / backward call made by this thread. */
 int evoattn_last_path(void);
