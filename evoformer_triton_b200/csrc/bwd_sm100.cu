@@ -38,7 +38,14 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int MASK_MIN = 0;
 constexpr int MASK_ADD = 1;
 
-template <int DP> struct GroupOf { static constexpr int G = (DP == 64) ? 2 : 4; };
+// G = MSA rows per CTA (each needs 2*DP TMEM columns for its dK/dV accumulators).  For DP <= 32
+// three rows leave 32+ columns for a dQ partial of its own, which lets the next step's S/dP
+// MMAs start while this step's dV/dK/dQ MMAs are still running; at DP = 64 the dQ partial has to
+// reuse the S columns.
+template <int DP> struct GroupOf {
+  static constexpr int G = (DP == 64) ? 2 : 3;
+  static constexpr bool kOwnDQ = (DP != 64);
+};
 
 template <int DP, int G>
 struct BwdSmem {
@@ -48,9 +55,9 @@ struct BwdSmem {
   static constexpr int kBiasChunk = BT * 128;
   static constexpr int offK = 0;                      // G tiles
   static constexpr int offV = offK + G * kTile;       // G tiles
-  static constexpr int offQ = offV + G * kTile;
-  static constexpr int offDO = offQ + kTile;
-  static constexpr int offP = offDO + kTile;
+  static constexpr int offQ = offV + G * kTile;        // 2 buffers
+  static constexpr int offDO = offQ + 2 * kTile;       // 2 buffers
+  static constexpr int offP = offDO + 2 * kTile;
   static constexpr int offDS = offP + kPS;
   static constexpr int offB = offDS + kPS;            // 2 chunk buffers
   static constexpr int offMask = offB + 2 * kBiasChunk;  // G x 128 floats
@@ -138,7 +145,10 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
   constexpr int HALF_D = DP / 2;
   constexpr int kTmemCols = 512;
   constexpr int colS = 0, colDP = BT, colDV = 2 * BT, colDK = 2 * BT + G * DP;
-  constexpr int colDQ = colS;  // the dQ partial reuses the S columns once S has been read
+  constexpr bool kOwnDQ = GroupOf<DP>::kOwnDQ;
+  // the dQ partial has columns of its own, or reuses the S columns once S has been read
+  constexpr int colDQ = kOwnDQ ? (2 * BT + 2 * G * DP) : colS;
+  static_assert(colDQ + DP <= kTmemCols, "TMEM budget");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -152,7 +162,7 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
   float* sMask = reinterpret_cast<float*>(smem + L::offMask);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBars);
   uint64_t* bar_kv = bars + 0;
-  uint64_t* bar_ld = bars + 1;
+  uint64_t* bar_ld = bars + 6;  // [2], one per Q/dO buffer
   uint64_t* bar_sdp = bars + 2;
   uint64_t* bar_out = bars + 3;
   uint64_t* bar_b = bars + 4;  // [2]
@@ -180,7 +190,7 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
   if (*abort_flag) return;
 
   if (tid == 0) {
-    mbar_init(bar_kv, 1); mbar_init(bar_ld, 1); mbar_init(bar_sdp, 1); mbar_init(bar_out, 1);
+    mbar_init(bar_kv, 1); mbar_init(bar_ld, 1); mbar_init(bar_ld + 1, 1); mbar_init(bar_sdp, 1); mbar_init(bar_out, 1);
     mbar_init(bar_b + 0, 1); mbar_init(bar_b + 1, 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
@@ -235,6 +245,37 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
   uint32_t step = 0, bias_phase = 0;
   const int total_steps = NT * ng;
 
+  // Step n = (query tile n / ng, MSA row n % ng).  Q and dO of step n live in buffer n & 1 and
+  // are fetched two steps ahead; S and dP of step n+1 are issued as soon as step n's have been
+  // read (right after step n's dV/dK/dQ MMAs when the dQ partial has TMEM columns of its own).
+  auto load_q_do = [&](int n) {
+    const int buf = n & 1;
+    mbar_expect_tx(bar_ld + buf, 2 * L::kTile);
+    tma_load_5d(sQ + buf * L::kTile, &tmQ, bar_ld + buf, 0, (n / ng) * BT, s0 + n % ng, h, b);
+    tma_load_5d(sDO + buf * L::kTile, &tmDO, bar_ld + buf, 0, (n / ng) * BT, s0 + n % ng, h, b);
+  };
+  auto issue_s_dp = [&](int n) {
+    const int buf = n & 1, g = n % ng;
+    mbar_wait(bar_ld + buf, (n >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+    tc_fence_after();
+    const uint32_t qa = smem_u32(sQ + buf * L::kTile), ka = smem_u32(sK + g * L::kTile);
+    const uint32_t da = smem_u32(sDO + buf * L::kTile), va = smem_u32(sV + g * L::kTile);
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk)
+      mma_ss(tmem + colS, make_sdesc(qa + kk * 32, 16, 8 * RB, SWZ), make_sdesc(ka + kk * 32, 16, 8 * RB, SWZ),
+             kIdescS, kk > 0 ? 1u : 0u);
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk)
+      mma_ss(tmem + colDP, make_sdesc(da + kk * 32, 16, 8 * RB, SWZ), make_sdesc(va + kk * 32, 16, 8 * RB, SWZ),
+             kIdescS, kk > 0 ? 1u : 0u);
+    mma_commit(bar_sdp);
+  };
+  if (tid == 0) {
+    load_q_do(0);
+    if (total_steps > 1) load_q_do(1);
+    issue_s_dp(0);
+  }
+
   for (int it = 0; it < NT; ++it) {
     const int i0 = it * BT;
     const int i = i0 + row;
@@ -245,32 +286,12 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
     for (int g = 0; g < ng; ++g, ++step) {
       const int s = s0 + g;
       const uint32_t ph = step & 1;
-      if (tid == 0) {
-        mbar_expect_tx(bar_ld, 2 * L::kTile);
-        tma_load_5d(sQ, &tmQ, bar_ld, 0, i0, s, h, b);
-        tma_load_5d(sDO, &tmDO, bar_ld, 0, i0, s, h, b);
-      }
       // row statistics of my query row
       float lse = 1e30f, delta = 0.f;
       if (i < a.R) {
         const long long ri = (((long long)b * a.H + h) * a.S + s) * a.R + i;
         lse = a.lse[ri];
         delta = a.delta[ri];
-      }
-      if (tid == 0) {
-        mbar_wait(bar_ld, ph, abort_flag, a.status, DEV_TIMEOUT_TMA);
-        tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + g * L::kTile);
-        const uint32_t da = smem_u32(sDO), va = smem_u32(sV + g * L::kTile);
-#pragma unroll
-        for (int kk = 0; kk < DP / 16; ++kk)
-          mma_ss(tmem + colS, make_sdesc(qa + kk * 32, 16, 8 * RB, SWZ), make_sdesc(ka + kk * 32, 16, 8 * RB, SWZ),
-                 kIdescS, kk > 0 ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < DP / 16; ++kk)
-          mma_ss(tmem + colDP, make_sdesc(da + kk * 32, 16, 8 * RB, SWZ), make_sdesc(va + kk * 32, 16, 8 * RB, SWZ),
-                 kIdescS, kk > 0 ? 1u : 0u);
-        mma_commit(bar_sdp);
       }
       const bool dead = (lse == -FLT_MAX);  // every key of this row was dropped: P is uniform
       const float nlse = -lse * kLog2e;
@@ -343,7 +364,8 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
       if (tid == 0) {
         tc_fence_after();
         const uint32_t pa = smem_u32(sP), dsa = smem_u32(sDS);
-        const uint32_t qa = smem_u32(sQ), da = smem_u32(sDO), ka = smem_u32(sK + g * L::kTile);
+        const uint32_t qa = smem_u32(sQ + (step & 1) * L::kTile), da = smem_u32(sDO + (step & 1) * L::kTile);
+        const uint32_t ka = smem_u32(sK + g * L::kTile);
         const uint32_t first = (it == 0) ? 0u : 1u;
         // dV_j[s] += P^T dO_i : A = P as MN-major (M = j), K runs over the 128 query rows
 #pragma unroll
@@ -361,6 +383,9 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
           mma_ss(tmem + colDQ, make_sdesc(dsa + (kk >> 2) * (BT * 128) + (kk & 3) * 32, 16, 1024, SWZ_128B),
                  make_sdesc(ka + kk * 16 * RB, 16, 8 * RB, SWZ), kIdescQ, kk > 0 ? 1u : 0u);
         mma_commit(bar_out);
+        // S and dP of this step have been read by everyone (barrier above): the next step's can
+        // start now, behind the MMAs just issued, unless its dQ partial shares the S columns.
+        if (kOwnDQ && step + 1 < (uint32_t)total_steps) issue_s_dp(step + 1);
       }
       mbar_wait(bar_out, ph, abort_flag, a.status, DEV_TIMEOUT_MMA);
       tc_fence_after();
@@ -377,8 +402,13 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
                          __uint_as_float(qr[d4 * 4 + 2]), __uint_as_float(qr[d4 * 4 + 3]));
         }
       }
-      tc_fence_before();
-      __syncthreads();  // Q/dO/P/dS buffers and the S columns may be overwritten now
+      // this step's MMAs are complete: its Q/dO buffer can take the step after next
+      if (tid == 0 && step + 2 < (uint32_t)total_steps) load_q_do(step + 2);
+      if (!kOwnDQ) {
+        tc_fence_before();
+        __syncthreads();  // the dQ partial (in the S columns) has been read by everyone
+        if (tid == 0 && step + 1 < (uint32_t)total_steps) issue_s_dp(step + 1);
+      }
     }
 
     // one reduction of this CTA's d_bias tile (i-tile, j-tile)
