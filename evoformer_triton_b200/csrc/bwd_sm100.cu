@@ -79,6 +79,13 @@ template <> struct Pack2<__half> {
   }
 };
 
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
@@ -459,6 +466,408 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Warp-specialised variant for DP <= 32 (384 threads): warps 0-7 compute exactly as above,
+// warp 8 is a control warp whose lane 0 issues every TMA load and every tcgen05.mma, so the
+// compute warps never stall on descriptor arithmetic or on a copy they have just asked for.
+//   * Q, dO, K, V tiles of a step arrive together, two steps ahead, in a two-deep ring;
+//   * pair-bias chunks (128x16 fp32) arrive in a two-deep ring per compute warpgroup, so the
+//     chunk after the one being read is always in flight;
+//   * P and dS are double-buffered in shared memory: once step n's are written the control warp
+//     issues S/dP of step n+1 and then dV/dK/dQ of step n, which run while the compute warps are
+//     already busy with step n+1; step n's dQ partial is folded into the fp32 accumulator at the
+//     end of step n+1.  (An MMA whose A operand comes from shared memory costs about as many
+//     cycles as its operand bytes / 64, so the 24 small dV/dK/dQ MMAs of a step take as long as
+//     two thirds of the step's arithmetic; they have to be hidden, not waited for.)
+// G = 3 rows per CTA: S 128 + dP 128 + 3*(dV 32 + dK 32) + dQ 32 = 480 TMEM columns.
+template <int DP>
+struct WsSmem {
+  static constexpr int G = 3;
+  static constexpr int RB = DP * 2;
+  static constexpr int kTile = BT * RB;
+  static constexpr int kPS = BT * BT * 2;
+  static constexpr int kBiasChunk = BT * 64;             // 128 rows x 16 fp32, 64-byte swizzle
+  static constexpr int kStage = 4 * kTile;               // Q, dO, K, V of one step
+  static constexpr int offStage = 0;                      // 2 stages
+  static constexpr int offP = offStage + 2 * kStage;      // 2 buffers
+  static constexpr int offDS = offP + 2 * kPS;            // 2 buffers
+  static constexpr int offB = offDS + 2 * kPS;            // [warpgroup][2] chunk buffers
+  static constexpr int offMask = offB + 4 * kBiasChunk;   // G x 128 floats
+  static constexpr int offBars = offMask + G * BT * 4;
+  static constexpr size_t bytes = offBars + 256 + 1024;
+};
+
+template <class T, int DP, int MASKMODE>
+__global__ void __launch_bounds__(384, 1)
+evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constant__ CUtensorMap tmQ,
+                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                  const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ CUtensorMap tmB) {
+  using L = WsSmem<DP>;
+  constexpr int G = L::G;
+  constexpr int RB = L::RB;
+  constexpr uint32_t SWZ = swizzle_code_for_row_bytes(RB);
+  constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr int HALF_D = DP / 2;
+  constexpr int kTmemCols = 512;
+  constexpr int colS = 0, colDP = BT, colDV = 2 * BT, colDK = 2 * BT + G * DP, colDQ = 2 * BT + 2 * G * DP;
+  static_assert(colDQ + DP <= kTmemCols, "TMEM budget");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sP = smem + L::offP;
+  uint8_t* sDS = smem + L::offDS;
+  uint8_t* sB = smem + L::offB;
+  float* sMask = reinterpret_cast<float*>(smem + L::offMask);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBars);
+  uint64_t* bar_ld = bars + 0;      // [2] tiles of a step landed
+  uint64_t* bar_sdp = bars + 2;     // S, dP of a step complete
+  uint64_t* bar_out = bars + 3;     // dV, dK, dQ MMAs of a step complete
+  uint64_t* bar_cdone = bars + 4;   // 256 compute threads finished a step (P, dS written; S, dP, dQ read)
+  uint64_t* bar_bfull = bars + 5;   // [2 warpgroups][2]
+  uint64_t* bar_bempty = bars + 9;  // [2 warpgroups][2], 128 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int NT = (a.R + BT - 1) / BT;
+  const int NC = (a.S + G - 1) / G;
+  int idx = blockIdx.x;
+  const int chunk = idx % NC; idx /= NC;
+  const int jt = idx % NT; idx /= NT;
+  const int h = idx % a.H;
+  const int b = idx / a.H;
+  const int s0 = chunk * G;
+  const int ng = min(G, a.S - s0);
+  const int j0 = jt * BT;
+  const bool has_bias = a.bias != nullptr;
+  const int total_steps = NT * ng;
+
+  if (tid == 0) *abort_flag = (a.status && *reinterpret_cast<volatile int*>(a.status) != 0) ? 1 : 0;
+  __syncthreads();
+  if (*abort_flag) return;
+
+  if (tid == 0) {
+    mbar_init(bar_ld, 1); mbar_init(bar_ld + 1, 1); mbar_init(bar_sdp, 1); mbar_init(bar_out, 1);
+    mbar_init(bar_cdone, 256);
+    for (int i = 0; i < 4; ++i) { mbar_init(bar_bfull + i, 1); mbar_init(bar_bempty + i, 128); }
+    fence_mbar_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
+    if (has_bias) prefetch_tmap(&tmB);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  for (int t = tid; t < G * BT; t += 384) {
+    const int g = t / BT, j = j0 + (t % BT);
+    float m;
+    if (j >= a.R || g >= ng) {
+      m = -FLT_MAX;
+    } else if (a.mask_kind == EVOATTN_MASK_NONE) {
+      m = (MASKMODE == MASK_MIN) ? FLT_MAX : 0.f;
+    } else {
+      const long long mi = (long long)b * a.smask.a + (long long)(s0 + g) * a.smask.b + (long long)j * a.smask.c;
+      if (MASKMODE == MASK_MIN) m = reinterpret_cast<const unsigned char*>(a.mask)[mi] ? FLT_MAX : -FLT_MAX;
+      else if (a.mask_kind == EVOATTN_MASK_ADD_F32) m = reinterpret_cast<const float*>(a.mask)[mi];
+      else m = to_float<T>(reinterpret_cast<const T*>(a.mask)[mi]);
+    }
+    sMask[t] = m;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp >= 8) {
+    setmaxnreg_dec<24>();
+    if (warp == 8) {
+      const uint32_t leader = (lane == 0) ? 1u : 0u;  // the lane that issues; everything else is warp-uniform
+      // =============================== control: TMA + MMA ===============================
+      constexpr uint32_t kIdescS = make_idesc(kBf16, false, false, BT, BT);  // S, dP: K-major operands
+      constexpr uint32_t kIdescT = make_idesc(kBf16, true, true, BT, DP);    // dV, dK: A = P^T / dS^T (MN-major)
+      constexpr uint32_t kIdescQ = make_idesc(kBf16, false, true, BT, DP);   // dQ: A = dS K-major, B = K MN-major
+      constexpr uint32_t kHiOp = static_cast<uint32_t>(make_sdesc_const(16, 8 * RB, SWZ) >> 32);
+      constexpr uint32_t kHiPS = static_cast<uint32_t>(make_sdesc_const(16, 1024, SWZ_128B) >> 32);
+      constexpr uint32_t kLoLbo = static_cast<uint32_t>(make_sdesc_const(16, 0, 0) & 0xffffffffu);
+      constexpr uint32_t kLoLboT = static_cast<uint32_t>(make_sdesc_const(BT * 128, 0, 0) & 0xffffffffu);
+      const uint32_t st_lo = smem_u32(smem + L::offStage) >> 4;
+      const uint32_t p_lo0 = smem_u32(sP) >> 4, ds_lo0 = smem_u32(sDS) >> 4;
+
+      auto load_step = [&](int n) {
+        const int buf = n & 1, it = n / ng, s = s0 + n % ng;
+        uint8_t* dst = smem + L::offStage + buf * L::kStage;
+        mbar_expect_tx_if(leader, bar_ld + buf, L::kStage);
+        tma_load_5d_if(leader, dst, &tmQ, bar_ld + buf, 0, it * BT, s, h, b);
+        tma_load_5d_if(leader, dst + L::kTile, &tmDO, bar_ld + buf, 0, it * BT, s, h, b);
+        tma_load_5d_if(leader, dst + 2 * L::kTile, &tmK, bar_ld + buf, 0, j0, s, h, b);
+        tma_load_5d_if(leader, dst + 3 * L::kTile, &tmV, bar_ld + buf, 0, j0, s, h, b);
+      };
+      // Bias chunk c (0..7, 16 columns each) of step n; chunks 0-3 belong to warpgroup 0, 4-7 to
+      // warpgroup 1, and each warpgroup cycles through its two buffers.
+      auto load_bias = [&](int n, int c) {
+        const int wgc = c >> 2;
+        const uint32_t seq = (uint32_t)n * 4 + (c & 3);  // running chunk index of that warpgroup
+        const int slot = wgc * 2 + (seq & 1);
+        mbar_wait(bar_bempty + slot, ((seq >> 1) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+        mbar_expect_tx_if(leader, bar_bfull + slot, L::kBiasChunk);
+        tma_load_4d_if(leader, sB + slot * L::kBiasChunk, &tmB, bar_bfull + slot, j0 + c * 16, (n / ng) * BT, h, b);
+      };
+      auto issue_s_dp = [&](int n) {
+        const int buf = n & 1;
+        mbar_wait(bar_ld + buf, (n >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        tc_fence_after();
+        const uint32_t base = (st_lo + buf * (L::kStage >> 4)) | kLoLbo;
+        const uint32_t qa = base, da = base + (L::kTile >> 4), ka = base + 2 * (L::kTile >> 4),
+                       va = base + 3 * (L::kTile >> 4);
+#pragma unroll
+        for (int kk = 0; kk < DP / 16; ++kk)
+          mma_ss_if(leader, tmem + colS, pack_desc(qa + kk * 2, kHiOp), pack_desc(ka + kk * 2, kHiOp), kIdescS, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < DP / 16; ++kk)
+          mma_ss_if(leader, tmem + colDP, pack_desc(da + kk * 2, kHiOp), pack_desc(va + kk * 2, kHiOp), kIdescS, kk > 0 ? 1u : 0u);
+        mma_commit_if(leader, bar_sdp);
+      };
+      auto issue_out = [&](int n) {
+        const int buf = n & 1, g = n % ng;
+        const uint32_t first = (n / ng == 0) ? 0u : 1u;
+        const uint32_t base = (st_lo + buf * (L::kStage >> 4)) | kLoLbo;
+        const uint32_t qa = base, da = base + (L::kTile >> 4), ka = base + 2 * (L::kTile >> 4);
+        const uint32_t p_lo = p_lo0 + buf * (L::kPS >> 4), ds_lo = ds_lo0 + buf * (L::kPS >> 4);
+        // dV_j[s] += P^T dO_i : A = P read MN-major (M = j); K runs over the 128 query rows
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)
+          mma_ss_if(leader, tmem + colDV + g * DP, pack_desc((p_lo + kk * 128) | kLoLboT, kHiPS), pack_desc(da + kk * RB, kHiOp),
+                 kIdescT, (kk > 0) ? 1u : first);
+        // dK_j[s] += dS^T Q_i
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)
+          mma_ss_if(leader, tmem + colDK + g * DP, pack_desc((ds_lo + kk * 128) | kLoLboT, kHiPS), pack_desc(qa + kk * RB, kHiOp),
+                 kIdescT, (kk > 0) ? 1u : first);
+        // dQ_i[s] partial = dS K_j : A = dS K-major (K runs over the 128 keys)
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)
+          mma_ss_if(leader, tmem + colDQ, pack_desc((ds_lo + (kk >> 2) * (BT * 128 >> 4) + (kk & 3) * 2) | kLoLbo, kHiPS),
+                 pack_desc(ka + kk * RB, kHiOp), kIdescQ, kk > 0 ? 1u : 0u);
+        mma_commit_if(leader, bar_out);
+      };
+
+      // Bias chunk k (0..3) of step n for both warpgroups.  A request waits until its buffer has
+      // been read (two chunks earlier), so requests are placed where that has already happened
+      // or is about to: the compute warps read chunk k of a step a quarter of the way apart.
+      auto bias_pair = [&](int n, int k) {
+        if (has_bias && n < total_steps) {
+          load_bias(n, k);
+          load_bias(n, 4 + k);
+        }
+      };
+      load_step(0);
+      if (total_steps > 1) load_step(1);
+      bias_pair(0, 0);
+      bias_pair(0, 1);
+      issue_s_dp(0);
+      bias_pair(0, 2);
+      bias_pair(0, 3);
+      bias_pair(1, 0);
+      bias_pair(1, 1);
+      for (int n = 0; n < total_steps; ++n) {
+        mbar_wait(bar_cdone, n & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+        tc_fence_after();
+        if (n + 1 < total_steps) issue_s_dp(n + 1);  // first: the compute warps wait for this one
+        issue_out(n);                                 // runs underneath step n+1's arithmetic
+        bias_pair(n + 1, 2);
+        bias_pair(n + 1, 3);
+        if (n + 2 < total_steps) {
+          // the stage of step n is free once its MMAs have completed
+          mbar_wait(bar_out, n & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
+          load_step(n + 2);
+        }
+        bias_pair(n + 2, 0);
+        bias_pair(n + 2, 1);
+      }
+    }
+  } else {
+    // =============================== compute warps ===============================
+    setmaxnreg_inc<240>();
+    const int wg = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t t_lane = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const float scale = a.scale;
+    const float inv_r = 1.f / (float)a.R;
+    uint32_t step = 0, bseq = 0;
+
+    auto fold_dq = [&](int n) {  // dQ partial of step n -> fp32 accumulator in global memory
+      mbar_wait(bar_out, n & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
+      tc_fence_after();
+      uint32_t qr[HALF_D];
+      tmem_ld<HALF_D>(t_lane + colDQ + wg * HALF_D, qr);
+      tmem_wait_ld();
+      const int i = (n / ng) * BT + row, s = s0 + n % ng;
+      if (i < a.R) {
+        float* dst = dq_acc + ((((long long)b * a.H + h) * a.S + s) * a.R + i) * a.D + wg * HALF_D;
+#pragma unroll
+        for (int d4 = 0; d4 < HALF_D / 4; ++d4)
+          if (wg * HALF_D + d4 * 4 < a.D)
+            red_add_v4(dst + d4 * 4, __uint_as_float(qr[d4 * 4]), __uint_as_float(qr[d4 * 4 + 1]),
+                       __uint_as_float(qr[d4 * 4 + 2]), __uint_as_float(qr[d4 * 4 + 3]));
+      }
+    };
+
+    // log-sum-exp and delta of this thread's query row for step n (out-of-range rows get a
+    // huge lse so that their P is exactly 0)
+    float lse_next = 1e30f, delta_next = 0.f;
+    auto load_row_stats = [&](int n) {
+      lse_next = 1e30f;
+      delta_next = 0.f;
+      const int i = (n / ng) * BT + row;
+      if (n < total_steps && i < a.R) {
+        const long long ri = (((long long)b * a.H + h) * a.S + s0 + n % ng) * a.R + i;
+        lse_next = a.lse[ri];
+        delta_next = a.delta[ri];
+      }
+    };
+    load_row_stats(0);
+
+    for (int it = 0; it < NT; ++it) {
+      const int i = it * BT + row;
+      float bacc[64];
+#pragma unroll
+      for (int e = 0; e < 64; ++e) bacc[e] = 0.f;
+
+      for (int g = 0; g < ng; ++g, ++step) {
+        const float lse = lse_next, delta = delta_next;  // fetched during the previous step
+        load_row_stats(step + 1);                         // in flight during this one
+        const bool dead = (lse == -FLT_MAX);  // every key of this row was dropped: P is uniform
+        const float nlse = -lse * kLog2e;
+        mbar_wait(bar_sdp, step & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
+        tc_fence_after();
+
+        uint8_t* prow = sP + (step & 1) * L::kPS + wg * (BT * 128) + row * 128;
+        uint8_t* drow = sDS + (step & 1) * L::kPS + wg * (BT * 128) + row * 128;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = wg * 64 + c * 32;
+          uint32_t sr[32], dr[32];
+          tmem_ld32(t_lane + colS + col0, sr);
+          tmem_ld32(t_lane + colDP + col0, dr);
+          tmem_wait_ld();
+          const float* mrow = sMask + g * BT + col0;
+#pragma unroll
+          for (int h16 = 0; h16 < 2; ++h16, ++bseq) {
+            // pair-bias chunk: my row's 16 floats (64 bytes, 64-byte swizzle)
+            float bv[16];
+            if (has_bias) {
+              const int slot = wg * 2 + (bseq & 1);
+              mbar_wait(bar_bfull + slot, (bseq >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+              const uint8_t* brow = sB + slot * L::kBiasChunk + row * 64;
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const float4 f = *reinterpret_cast<const float4*>(brow + ((q4 ^ ((row >> 1) & 3)) << 4));
+                bv[q4 * 4 + 0] = f.x; bv[q4 * 4 + 1] = f.y; bv[q4 * 4 + 2] = f.z; bv[q4 * 4 + 3] = f.w;
+              }
+              mbar_arrive(bar_bempty + slot);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) bv[e] = 0.f;
+            }
+#pragma unroll
+            for (int c8 = 0; c8 < 2; ++c8) {
+              const int e0 = h16 * 16 + c8 * 8;  // first of eight columns inside this 32-column block
+              float p[8], ds[8];
+              const float4 mk0 = *reinterpret_cast<const float4*>(mrow + e0);
+              const float4 mk1 = *reinterpret_cast<const float4*>(mrow + e0 + 4);
+              const float mkv[8] = {mk0.x, mk0.y, mk0.z, mk0.w, mk1.x, mk1.y, mk1.z, mk1.w};
+              if (!dead) {
+                float x[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) x[u] = fmaf(__uint_as_float(sr[e0 + u]), scale, bv[c8 * 8 + u]);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) x[u] = (MASKMODE == MASK_MIN) ? fminf(x[u], mkv[u]) : (x[u] + mkv[u]);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) x[u] = fmaf(x[u], kLog2e, nlse);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) p[u] = ex2(x[u]);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) ds[u] = p[u] * (__uint_as_float(dr[e0 + u]) - delta);
+              } else {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                  p[u] = (j0 + col0 + e0 + u < a.R) ? inv_r : 0.f;
+                  ds[u] = 0.f;  // replaced scores are constants: no gradient flows through them
+                }
+              }
+#pragma unroll
+              for (int u = 0; u < 8; ++u) bacc[c * 32 + e0 + u] += ds[u];
+              uint4 pk, dk;
+              pk.x = Pack2<T>::pack(p[0], p[1]); pk.y = Pack2<T>::pack(p[2], p[3]);
+              pk.z = Pack2<T>::pack(p[4], p[5]); pk.w = Pack2<T>::pack(p[6], p[7]);
+              dk.x = Pack2<T>::pack(ds[0], ds[1]); dk.y = Pack2<T>::pack(ds[2], ds[3]);
+              dk.z = Pack2<T>::pack(ds[4], ds[5]); dk.w = Pack2<T>::pack(ds[6], ds[7]);
+              const int chunk16 = ((c * 4 + h16 * 2 + c8) ^ (row & 7)) << 4;
+              *reinterpret_cast<uint4*>(prow + chunk16) = pk;
+              *reinterpret_cast<uint4*>(drow + chunk16) = dk;
+            }
+          }
+        }
+        // the previous step's dQ partial: its MMAs ran underneath this step's arithmetic, and it
+        // must be out of TMEM before the control warp may issue this step's dQ MMA
+        if (step > 0) fold_dq(step - 1);
+        tc_fence_before();
+        fence_async_shared();
+        mbar_arrive(bar_cdone);  // P, dS of this step are in shared memory; S, dP, dQ have been read
+      }
+
+      // one reduction of this CTA's d_bias tile (i-tile, j-tile)
+      if (has_bias && i < a.R) {
+        float* dst = a.dbias + (((long long)b * a.H + h) * a.R + i) * a.R + j0 + wg * 64;
+#pragma unroll
+        for (int e4 = 0; e4 < 16; ++e4)
+          if (j0 + wg * 64 + e4 * 4 < a.R)
+            red_add_v4(dst + e4 * 4, bacc[e4 * 4], bacc[e4 * 4 + 1], bacc[e4 * 4 + 2], bacc[e4 * 4 + 3]);
+      }
+    }
+
+    fold_dq(total_steps - 1);  // also the point where every MMA of this CTA has completed
+
+    // ---- dK, dV of the G rows: TMEM -> registers -> global
+    const int j = j0 + row;
+    for (int g = 0; g < ng; ++g) {
+      uint32_t kr[HALF_D], vr[HALF_D];
+      tmem_ld<HALF_D>(t_lane + colDK + g * DP + wg * HALF_D, kr);
+      tmem_ld<HALF_D>(t_lane + colDV + g * DP + wg * HALF_D, vr);
+      tmem_wait_ld();
+      if (j < a.R) {
+        T* kd = reinterpret_cast<T*>(a.dk) + off4(a.sdk, b, h, s0 + g, j) + wg * HALF_D;
+        T* vd = reinterpret_cast<T*>(a.dv) + off4(a.sdv, b, h, s0 + g, j) + wg * HALF_D;
+#pragma unroll
+        for (int d8 = 0; d8 < HALF_D / 8; ++d8) {
+          if (wg * HALF_D + d8 * 8 < a.D) {
+            uint4 pk, pv;
+            pk.x = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 0]) * scale, __uint_as_float(kr[d8 * 8 + 1]) * scale);
+            pk.y = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 2]) * scale, __uint_as_float(kr[d8 * 8 + 3]) * scale);
+            pk.z = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 4]) * scale, __uint_as_float(kr[d8 * 8 + 5]) * scale);
+            pk.w = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 6]) * scale, __uint_as_float(kr[d8 * 8 + 7]) * scale);
+            pv.x = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 0]), __uint_as_float(vr[d8 * 8 + 1]));
+            pv.y = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 2]), __uint_as_float(vr[d8 * 8 + 3]));
+            pv.z = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 4]), __uint_as_float(vr[d8 * 8 + 5]));
+            pv.w = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 6]), __uint_as_float(vr[d8 * 8 + 7]));
+            *reinterpret_cast<uint4*>(kd + d8 * 8) = pk;
+            *reinterpret_cast<uint4*>(vd + d8 * 8) = pv;
+          }
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {}
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <class T, int DP>
@@ -479,7 +888,7 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (!make_qkv_map(&tv, a.v, a.sv, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tdo, a.d_o, a.sdo, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   if (a.bias) {
-    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT)) return EVOATTN_ERR_CUDA;
+    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, DP <= 32 ? 16 : 32)) return EVOATTN_ERR_CUDA;
   } else {
     tb = tq;
   }
@@ -489,13 +898,22 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
     return EVOATTN_ERR_CUDA;
   delta_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(a);
 
-  const int NT = (a.R + BT - 1) / BT, NC = (a.S + G - 1) / G;
-  const long long ctas = (long long)a.B * a.H * NT * NC;
+  const int NT = (a.R + BT - 1) / BT;
   const bool add = a.mask_kind == EVOATTN_MASK_ADD_F32 || a.mask_kind == EVOATTN_MASK_ADD_SAME;
-  auto kern = add ? evo_bwd_sm100_kernel<T, DP, MASK_ADD> : evo_bwd_sm100_kernel<T, DP, MASK_MIN>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::bytes) != cudaSuccess)
-    return EVOATTN_ERR_CUDA;
-  kern<<<(unsigned)ctas, kThreads, L::bytes, st>>>(a, dq_acc, tq, tk, tv, tdo, tb);
+  if constexpr (DP <= 32) {
+    using W = WsSmem<DP>;
+    const long long ctas = (long long)a.B * a.H * NT * ((a.S + W::G - 1) / W::G);
+    auto kern = add ? evo_bwd_ws_kernel<T, DP, MASK_ADD> : evo_bwd_ws_kernel<T, DP, MASK_MIN>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)W::bytes) != cudaSuccess)
+      return EVOATTN_ERR_CUDA;
+    kern<<<(unsigned)ctas, 384, W::bytes, st>>>(a, dq_acc, tq, tk, tv, tdo, tb);
+  } else {
+    const long long ctas = (long long)a.B * a.H * NT * ((a.S + G - 1) / G);
+    auto kern = add ? evo_bwd_sm100_kernel<T, DP, MASK_ADD> : evo_bwd_sm100_kernel<T, DP, MASK_MIN>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::bytes) != cudaSuccess)
+      return EVOATTN_ERR_CUDA;
+    kern<<<(unsigned)ctas, kThreads, L::bytes, st>>>(a, dq_acc, tq, tk, tv, tdo, tb);
+  }
   const long long n8 = (long long)rows * (a.D / 8);
   dq_convert_kernel<T><<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(a, dq_acc);
   *launches += 3;

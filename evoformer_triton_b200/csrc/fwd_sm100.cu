@@ -479,7 +479,7 @@ int launch_t(const Args& a, cudaStream_t st, int* launches) {
   if (!make_qkv_map(&tk, a.k, a.sk, a.B, a.H, a.S, a.R, a.D, DP, BN)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tv, a.v, a.sv, a.B, a.H, a.S, a.R, a.D, DP, BN)) return EVOATTN_ERR_CUDA;
   if (a.bias) {
-    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BM)) return EVOATTN_ERR_CUDA;
+    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BM, 32)) return EVOATTN_ERR_CUDA;
   } else {
     tb = tq;
   }

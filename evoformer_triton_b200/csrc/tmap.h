@@ -14,8 +14,9 @@ namespace evo {
 bool make_qkv_map(CUtensorMap* out, const void* base, const Str4& stride_elems, int B, int H, int S, int R, int D,
                   int box_d, int box_r);
 
-// fp32 [B,H,R,R] pair bias -> 4-D map with dims (R_j, R_i, H, B); box = (32, box_i, 1, 1),
-// 128-byte swizzle (one row of a box is 32 floats = 128 bytes).
-bool make_bias_map(CUtensorMap* out, const float* base, const Str3& stride_elems, int B, int H, int R, int box_i);
+// fp32 [B,H,R,R] pair bias -> 4-D map with dims (R_j, R_i, H, B); box = (box_j, box_i, 1, 1)
+// with box_j = 32 (rows of 128 bytes, 128-byte swizzle) or 16 (rows of 64 bytes, 64-byte swizzle).
+bool make_bias_map(CUtensorMap* out, const float* base, const Str3& stride_elems, int B, int H, int R, int box_i,
+                   int box_j);
 
 }  // namespace evo
