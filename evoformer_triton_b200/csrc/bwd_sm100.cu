@@ -523,9 +523,9 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
   uint64_t* bar_ld = bars + 0;      // [2] tiles of a step landed
   uint64_t* bar_sdp = bars + 2;     // S, dP of a step complete
   uint64_t* bar_out = bars + 3;     // dV, dK, dQ MMAs of a step complete
-  uint64_t* bar_cdone = bars + 4;   // 256 compute threads finished a step (P, dS written; S, dP, dQ read)
+  uint64_t* bar_cdone = bars + 4;   // the 8 compute warps finished a step (P, dS written; S, dP, dQ read)
   uint64_t* bar_bfull = bars + 5;   // [2 warpgroups][2]
-  uint64_t* bar_bempty = bars + 9;  // [2 warpgroups][2], 128 arrivals
+  uint64_t* bar_bempty = bars + 9;  // [2 warpgroups][2], one arrival per warp
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
 
@@ -549,8 +549,8 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
 
   if (tid == 0) {
     mbar_init(bar_ld, 1); mbar_init(bar_ld + 1, 1); mbar_init(bar_sdp, 1); mbar_init(bar_out, 1);
-    mbar_init(bar_cdone, 256);
-    for (int i = 0; i < 4; ++i) { mbar_init(bar_bfull + i, 1); mbar_init(bar_bempty + i, 128); }
+    mbar_init(bar_cdone, 8);   // one arrival per compute warp
+    for (int i = 0; i < 4; ++i) { mbar_init(bar_bfull + i, 1); mbar_init(bar_bempty + i, 4); }
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
     if (has_bias) prefetch_tmap(&tmB);
@@ -694,6 +694,7 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
     const uint32_t t_lane = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const float scale = a.scale;
     const float inv_r = 1.f / (float)a.R;
+    const F2 scale2 = f2_make(scale, scale), l2e2 = f2_make(kLog2e, kLog2e);
     uint32_t step = 0, bseq = 0;
 
     auto fold_dq = [&](int n) {  // dQ partial of step n -> fp32 accumulator in global memory
@@ -739,6 +740,7 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
         load_row_stats(step + 1);                         // in flight during this one
         const bool dead = (lse == -FLT_MAX);  // every key of this row was dropped: P is uniform
         const float nlse = -lse * kLog2e;
+        const F2 nlse2 = f2_make(nlse, nlse), delta2 = f2_make(delta, delta);
         mbar_wait(bar_sdp, step & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
         tc_fence_after();
 
@@ -765,7 +767,8 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
                 const float4 f = *reinterpret_cast<const float4*>(brow + ((q4 ^ ((row >> 1) & 3)) << 4));
                 bv[q4 * 4 + 0] = f.x; bv[q4 * 4 + 1] = f.y; bv[q4 * 4 + 2] = f.z; bv[q4 * 4 + 3] = f.w;
               }
-              mbar_arrive(bar_bempty + slot);
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar_bempty + slot);  // one arrival per warp
             } else {
 #pragma unroll
               for (int e = 0; e < 16; ++e) bv[e] = 0.f;
@@ -780,15 +783,22 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
               if (!dead) {
                 float x[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) x[u] = fmaf(__uint_as_float(sr[e0 + u]), scale, bv[c8 * 8 + u]);
+                for (int u = 0; u < 8; u += 2)  // x = scale*S + bias, two elements per instruction
+                  f2_get(f2_fma(f2_from_bits(sr[e0 + u], sr[e0 + u + 1]), scale2, f2_make(bv[c8 * 8 + u], bv[c8 * 8 + u + 1])),
+                         x[u], x[u + 1]);
 #pragma unroll
                 for (int u = 0; u < 8; ++u) x[u] = (MASKMODE == MASK_MIN) ? fminf(x[u], mkv[u]) : (x[u] + mkv[u]);
 #pragma unroll
-                for (int u = 0; u < 8; ++u) x[u] = fmaf(x[u], kLog2e, nlse);
+                for (int u = 0; u < 8; u += 2) f2_get(f2_fma(f2_make(x[u], x[u + 1]), l2e2, nlse2), x[u], x[u + 1]);
 #pragma unroll
                 for (int u = 0; u < 8; ++u) p[u] = ex2(x[u]);
 #pragma unroll
-                for (int u = 0; u < 8; ++u) ds[u] = p[u] * (__uint_as_float(dr[e0 + u]) - delta);
+                for (int u = 0; u < 8; u += 2) {  // dS = P (dP - delta); d_bias_acc += dS
+                  const F2 t = f2_mul(f2_make(p[u], p[u + 1]), f2_sub(f2_from_bits(dr[e0 + u], dr[e0 + u + 1]), delta2));
+                  f2_get(t, ds[u], ds[u + 1]);
+                  f2_get(f2_add(f2_make(bacc[c * 32 + e0 + u], bacc[c * 32 + e0 + u + 1]), t), bacc[c * 32 + e0 + u],
+                         bacc[c * 32 + e0 + u + 1]);
+                }
               } else {
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
@@ -796,8 +806,6 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
                   ds[u] = 0.f;  // replaced scores are constants: no gradient flows through them
                 }
               }
-#pragma unroll
-              for (int u = 0; u < 8; ++u) bacc[c * 32 + e0 + u] += ds[u];
               uint4 pk, dk;
               pk.x = Pack2<T>::pack(p[0], p[1]); pk.y = Pack2<T>::pack(p[2], p[3]);
               pk.z = Pack2<T>::pack(p[4], p[5]); pk.w = Pack2<T>::pack(p[6], p[7]);
@@ -814,7 +822,8 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
         if (step > 0) fold_dq(step - 1);
         tc_fence_before();
         fence_async_shared();
-        mbar_arrive(bar_cdone);  // P, dS of this step are in shared memory; S, dP, dQ have been read
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_cdone);  // P, dS of this step are in shared memory; S, dP, dQ have been read
       }
 
       // one reduction of this CTA's d_bias tile (i-tile, j-tile)

@@ -151,11 +151,11 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         mbar_init(v_full(w, st), 1); mbar_init(v_empty(w, st), 1);
       }
       mbar_init(s_full(w, 0), 1); mbar_init(s_full(w, 1), 1);
-      mbar_init(p_full(w), 128);
+      mbar_init(p_full(w), 4);  // one arrival per softmax warp
       mbar_init(o_full(w, 0), 1); mbar_init(o_full(w, 1), 1);
-      for (int st = 0; st < 2; ++st) { mbar_init(m_full(w, st), 32); mbar_init(m_empty(w, st), 128); }
+      for (int st = 0; st < 2; ++st) { mbar_init(m_full(w, st), 1); mbar_init(m_empty(w, st), 4); }
     }
-    for (int st = 0; st < BST; ++st) { mbar_init(b_full(st), 1); mbar_init(b_empty(st), 256); }
+    for (int st = 0; st < BST; ++st) { mbar_init(b_full(st), 1); mbar_init(b_empty(st), 8); }
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
     if (has_bias) prefetch_tmap(&tmB);
@@ -286,7 +286,8 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
             }
             dst[j] = m;
           }
-          mbar_arrive(m_full(w, st));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(m_full(w, st));
         }
       }
     }
@@ -297,6 +298,7 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
     const int row = (warp & 3) * 32 + lane;
     const uint32_t t_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + w * C::tmemWg;
     const float scale = a.scale;
+    const F2 scale2 = f2_make(scale, scale);
     uint32_t g = 0, n_item = 0;  // running key-tile and item index
     // The two warpgroups take turns in the exponential phase (named barriers 1 and 2 pass a
     // token back and forth): while one keeps the MUFU busy, the other runs its load / bias /
@@ -332,9 +334,9 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         // independent elements (loads, FMAs, mins, then eight separate max chains) so that the
         // in-order issue never waits on the previous instruction's result.
         float x[BN];
-        float mx8[8];
+        float mx8[4];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) mx8[u] = -FLT_MAX;
+        for (int u = 0; u < 4; ++u) mx8[u] = -FLT_MAX;
         uint32_t sr[BN];
         tmem_ld32(t_base + (g & 1) * BN, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
         tmem_ld32(t_base + (g & 1) * BN + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
@@ -353,18 +355,24 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
           const float mkv[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
           float v[8];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) v[u] = fmaf(__uint_as_float(sr[g8 * 8 + u]), scale, bvv[u]);
+          for (int u = 0; u < 8; u += 2) {  // x = scale*S + bias, two elements per instruction
+            const F2 t = f2_fma(f2_from_bits(sr[g8 * 8 + u], sr[g8 * 8 + u + 1]), scale2, f2_make(bvv[u], bvv[u + 1]));
+            f2_get(t, v[u], v[u + 1]);
+          }
 #pragma unroll
           for (int u = 0; u < 8; ++u) v[u] = (MASKMODE == MASK_MIN) ? fminf(v[u], mkv[u]) : (v[u] + mkv[u]);
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
+          for (int u = 0; u < 8; u += 2) {
             x[g8 * 8 + u] = v[u];
-            mx8[u] = fmaxf(mx8[u], v[u]);
+            x[g8 * 8 + u + 1] = v[u + 1];
+            mx8[u >> 1] = max3(mx8[u >> 1], v[u], v[u + 1]);
           }
         }
-        const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                               fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-        if (has_bias) mbar_arrive(b_empty(g % BST));
+        const float mx = fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3]));
+        if (has_bias) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(b_empty(g % BST));  // one arrival per warp
+        }
 
         const float m_new = fmaxf(m_run, mx);
         const float alpha = ex2((m_run - m_new) * kLog2e);
@@ -373,21 +381,28 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         named_bar_sync(1 + w, 256);  // my turn on the exponential unit
         if (m_new != -FLT_MAX) {
           const float nm2 = -m_new * kLog2e;
-          float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+          const F2 l2e2 = f2_make(kLog2e, kLog2e), nm22 = f2_make(nm2, nm2);
+          F2 ls4[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) ls4[u] = f2_make(0.f, 0.f);
 #pragma unroll
           for (int g8 = 0; g8 < BN / 8; ++g8) {
             float y[8], p[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) y[u] = fmaf(x[g8 * 8 + u], kLog2e, nm2);
+            for (int u = 0; u < 8; u += 2)
+              f2_get(f2_fma(f2_make(x[g8 * 8 + u], x[g8 * 8 + u + 1]), l2e2, nm22), y[u], y[u + 1]);
 #pragma unroll
             for (int u = 0; u < 8; ++u) p[u] = ex2(y[u]);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              ls4[u] += p[2 * u] + p[2 * u + 1];
+              ls4[u] = f2_add(ls4[u], f2_make(p[2 * u], p[2 * u + 1]));
               pk[g8 * 4 + u] = Pack2<T>::pack(p[2 * u], p[2 * u + 1]);
             }
           }
-          lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+          float lsa[8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) f2_get(ls4[u], lsa[2 * u], lsa[2 * u + 1]);
+          lsum = ((lsa[0] + lsa[1]) + (lsa[2] + lsa[3])) + ((lsa[4] + lsa[5]) + (lsa[6] + lsa[7]));
         } else {
           // every key seen so far was dropped: the scores are all -FLT_MAX and the softmax is
           // uniform over the real keys (test.py:54-55 semantics)
@@ -412,8 +427,10 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
           if constexpr (DP == 64)
             tmem_ld32(t_base + 2 * BN + ((g - 1) & 1) * DP + 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[32]));
           tmem_wait_ld();
+          const F2 ap2 = f2_make(alpha_pending, alpha_pending);
 #pragma unroll
-          for (int d = 0; d < DP; ++d) acc[d] = fmaf(acc[d], alpha_pending, __uint_as_float(orr[d]));
+          for (int d = 0; d < DP; d += 2)
+            f2_get(f2_fma(f2_make(acc[d], acc[d + 1]), ap2, f2_from_bits(orr[d], orr[d + 1])), acc[d], acc[d + 1]);
         }
         alpha_pending = alpha;
 
@@ -423,7 +440,8 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         tmem_st32(t_base + (g & 1) * BN, pk);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(p_full(w));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full(w));
       }
       // last tile's P V
       {
@@ -454,7 +472,8 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         const long long li = (((long long)it.b * a.H + it.h) * a.S + s) * a.R + i;
         a.lse[li] = (m_run == -FLT_MAX) ? -FLT_MAX : (m_run + logf(l_run));
       }
-      mbar_arrive(m_empty(w, mst));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(m_empty(w, mst));
     }
     if (w == 0) named_bar_sync(1, 256);  // consume the last token so no arrival is left pending
   }
