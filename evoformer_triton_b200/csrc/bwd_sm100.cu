@@ -502,7 +502,8 @@ template <class T, int DP, int MASKMODE>
 __global__ void __launch_bounds__(384, 1)
 evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constant__ CUtensorMap tmQ,
                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                  const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ CUtensorMap tmB) {
+                  const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmDB) {
   using L = WsSmem<DP>;
   constexpr int G = L::G;
   constexpr int RB = L::RB;
@@ -826,17 +827,34 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
         if (lane == 0) mbar_arrive(bar_cdone);  // P, dS of this step are in shared memory; S, dP, dQ have been read
       }
 
-      // one reduction of this CTA's d_bias tile (i-tile, j-tile)
-      if (has_bias && i < a.R) {
-        float* dst = a.dbias + (((long long)b * a.H + h) * a.R + i) * a.R + j0 + wg * 64;
+      // One reduction of this CTA's d_bias tile (i-tile, j-tile): the 128x128 fp32 tile is staged
+      // in the P/dS buffer pair that the next step will use (its last readers, the MMAs of step
+      // `step-2`, have completed: their dQ partial was folded above) as four 128x32 boxes in the
+      // 128-byte-swizzled layout and added to global memory by four bulk tensor reductions.
+      if (has_bias) {
+        uint8_t* stage = ((wg == 0) ? sP : sDS) + (step & 1) * L::kPS + row * 128;  // `step` is already the next step
 #pragma unroll
-        for (int e4 = 0; e4 < 16; ++e4)
-          if (j0 + wg * 64 + e4 * 4 < a.R)
-            red_add_v4(dst + e4 * 4, bacc[e4 * 4], bacc[e4 * 4 + 1], bacc[e4 * 4 + 2], bacc[e4 * 4 + 3]);
+        for (int bx = 0; bx < 2; ++bx)
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            *reinterpret_cast<float4*>(stage + bx * (BT * 128) + ((q4 ^ (row & 7)) << 4)) =
+                make_float4(bacc[bx * 32 + q4 * 4], bacc[bx * 32 + q4 * 4 + 1], bacc[bx * 32 + q4 * 4 + 2],
+                            bacc[bx * 32 + q4 * 4 + 3]);
+        fence_async_shared();
+        named_bar_sync(1 + wg, 128);
+        if ((tid & 127) == 0) {
+          const uint8_t* src = ((wg == 0) ? sP : sDS) + (step & 1) * L::kPS;
+          tma_reduce_add_4d(&tmDB, src, j0 + wg * 64, it * BT, h, b);
+          tma_reduce_add_4d(&tmDB, src + BT * 128, j0 + wg * 64 + 32, it * BT, h, b);
+          tma_commit_group();
+          tma_wait_group_read0();  // the staging buffer may be overwritten once it has been read
+        }
+        named_bar_sync(1 + wg, 128);
       }
     }
 
     fold_dq(total_steps - 1);  // also the point where every MMA of this CTA has completed
+    if (has_bias && (tid & 127) == 0) tma_wait_group0();
 
     // ---- dK, dV of the G rows: TMEM -> registers -> global
     const int j = j0 + row;
@@ -896,10 +914,14 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (!make_qkv_map(&tk, a.k, a.sk, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tv, a.v, a.sv, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tdo, a.d_o, a.sdo, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
+  CUtensorMap tdb;
   if (a.bias) {
     if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, DP <= 32 ? 16 : 32)) return EVOATTN_ERR_CUDA;
+    const Str3 dense{(long long)a.H * a.R * a.R, (long long)a.R * a.R, (long long)a.R};
+    if (!make_bias_map(&tdb, a.dbias, dense, a.B, a.H, a.R, BT, 32)) return EVOATTN_ERR_CUDA;
   } else {
     tb = tq;
+    tdb = tq;
   }
   if (cudaMemsetAsync(dq_acc, 0, dq_bytes, st) != cudaSuccess) return EVOATTN_ERR_CUDA;
   if (a.dbias &&
@@ -915,7 +937,7 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
     auto kern = add ? evo_bwd_ws_kernel<T, DP, MASK_ADD> : evo_bwd_ws_kernel<T, DP, MASK_MIN>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)W::bytes) != cudaSuccess)
       return EVOATTN_ERR_CUDA;
-    kern<<<(unsigned)ctas, 384, W::bytes, st>>>(a, dq_acc, tq, tk, tv, tdo, tb);
+    kern<<<(unsigned)ctas, 384, W::bytes, st>>>(a, dq_acc, tq, tk, tv, tdo, tb, tdb);
   } else {
     const long long ctas = (long long)a.B * a.H * NT * ((a.S + G - 1) / G);
     auto kern = add ? evo_bwd_sm100_kernel<T, DP, MASK_ADD> : evo_bwd_sm100_kernel<T, DP, MASK_MIN>;
