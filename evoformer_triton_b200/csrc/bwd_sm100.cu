@@ -20,6 +20,8 @@
 // P and dS (rounded to the storage type, as evoformer.py:459,603,611 do) are written once to
 // shared memory as [i][j] tiles in the 128B-swizzled layout and are read by the tensor core
 // both K-major (dQ = dS K) and MN-major (dV = P^T dO, dK = dS^T Q).
+#include <stdlib.h>
+
 #include <type_traits>
 
 #include "common.cuh"
@@ -419,7 +421,7 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
     }
 
     // one reduction of this CTA's d_bias tile (i-tile, j-tile)
-    if (has_bias && i < a.R) {
+    if (a.dbias != nullptr && i < a.R) {
       float* dst = a.dbias + (((long long)b * a.H + h) * a.R + i) * a.R + j0 + wg * 64;
 #pragma unroll
       for (int e4 = 0; e4 < 16; ++e4)
@@ -831,7 +833,7 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
       // in the P/dS buffer pair that the next step will use (its last readers, the MMAs of step
       // `step-2`, have completed: their dQ partial was folded above) as four 128x32 boxes in the
       // 128-byte-swizzled layout and added to global memory by four bulk tensor reductions.
-      if (has_bias) {
+      if (a.dbias != nullptr) {
         uint8_t* stage = ((wg == 0) ? sP : sDS) + (step & 1) * L::kPS + row * 128;  // `step` is already the next step
 #pragma unroll
         for (int bx = 0; bx < 2; ++bx)
@@ -854,7 +856,7 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
     }
 
     fold_dq(total_steps - 1);  // also the point where every MMA of this CTA has completed
-    if (has_bias && (tid & 127) == 0) tma_wait_group0();
+    if (a.dbias != nullptr && (tid & 127) == 0) tma_wait_group0();
 
     // ---- dK, dV of the G rows: TMEM -> registers -> global
     const int j = j0 + row;
@@ -897,11 +899,26 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const __grid_constan
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// d(pair_bias) either leaves the fused kernel through fp32 reductions (one 64 KB tile per CTA and
+// query tile) or is produced by the separate kernel of dbias_sm100.cu, which recomputes S and dP
+// but adds almost nothing to global memory.  On B200 the fused form measures faster for every
+// benchmark configuration (the recomputation costs more than the reductions), so the separate
+// kernel is opt-in: EVOATTN_SPLIT_DBIAS=1.
+bool split_dbias(const Args& a) {
+  static const bool want_split = [] {
+    const char* e = getenv("EVOATTN_SPLIT_DBIAS");
+    return e && e[0] == '1';
+  }();
+  return a.dbias != nullptr && want_split;
+}
+
 template <class T, int DP>
 int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* launches) {
   constexpr int G = GroupOf<DP>::G;
   using L = BwdSmem<DP, G>;
   Args a = a0;
+  const bool split = split_dbias(a0);
+  if (split) a.dbias = nullptr;  // the fused kernel skips its d_bias reductions
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;
   const size_t delta_bytes = align_up(rows * sizeof(float), 256);
   const size_t dq_bytes = rows * a.D * sizeof(float);
@@ -918,7 +935,8 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (a.bias) {
     if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, DP <= 32 ? 16 : 32)) return EVOATTN_ERR_CUDA;
     const Str3 dense{(long long)a.H * a.R * a.R, (long long)a.R * a.R, (long long)a.R};
-    if (!make_bias_map(&tdb, a.dbias, dense, a.B, a.H, a.R, BT, 32)) return EVOATTN_ERR_CUDA;
+    if (!a.dbias) tdb = tq;  // d_bias comes from the separate kernel
+    else if (!make_bias_map(&tdb, a.dbias, dense, a.B, a.H, a.R, BT, 32)) return EVOATTN_ERR_CUDA;
   } else {
     tb = tq;
     tdb = tq;
@@ -928,6 +946,12 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
       cudaMemsetAsync(a.dbias, 0, (size_t)a.B * a.H * a.R * a.R * sizeof(float), st) != cudaSuccess)
     return EVOATTN_ERR_CUDA;
   delta_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(a);
+  if (split) {
+    Args ab = a;
+    ab.dbias = a0.dbias;
+    const int rc = launch_sm100_dbias(std::is_same<T, __nv_bfloat16>::value ? EVOATTN_BF16 : EVOATTN_FP16, ab, st, launches);
+    if (rc != EVOATTN_OK) return rc;
+  }
 
   const int NT = (a.R + BT - 1) / BT;
   const bool add = a.mask_kind == EVOATTN_MASK_ADD_F32 || a.mask_kind == EVOATTN_MASK_ADD_SAME;

@@ -82,6 +82,19 @@ __device__ __forceinline__ float apply_mask(float x, const void* mask, int kind,
   return x;
 }
 
+// Residue mask of key j for batch b, MSA row s as the float the tcgen05 kernels combine with a
+// score: MIN mode (boolean keep-mask or none) gives +FLT_MAX (keep) or -FLT_MAX (drop) for
+// `min(score, m)`; ADD mode gives the additive value.  Keys beyond R are always dropped.
+template <class T, int MIN_MODE>
+__device__ __forceinline__ float mask_value(const Args& a, int b, int s, int j) {
+  if (j >= a.R) return -FLT_MAX;
+  if (a.mask_kind == EVOATTN_MASK_NONE) return MIN_MODE ? FLT_MAX : 0.f;
+  const long long mi = (long long)b * a.smask.a + (long long)s * a.smask.b + (long long)j * a.smask.c;
+  if (MIN_MODE) return reinterpret_cast<const unsigned char*>(a.mask)[mi] ? FLT_MAX : -FLT_MAX;
+  if (a.mask_kind == EVOATTN_MASK_ADD_F32) return reinterpret_cast<const float*>(a.mask)[mi];
+  return to_float<T>(reinterpret_cast<const T*>(a.mask)[mi]);
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

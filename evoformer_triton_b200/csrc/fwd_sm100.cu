@@ -272,19 +272,15 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
           const int s = min(2 * it.sp + w, a.S - 1);
           mbar_wait(m_empty(w, st), ((n >> 1) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
           float* dst = sMask + (w * 2 + st) * r_pad;
-          for (int j = lane; j < r_pad; j += 32) {
-            float m;
-            if (j >= a.R) {
-              m = -FLT_MAX;
-            } else if (a.mask_kind == EVOATTN_MASK_NONE) {
-              m = (MASKMODE == MASK_MIN) ? FLT_MAX : 0.f;
-            } else {
-              const long long mi = (long long)it.b * a.smask.a + (long long)s * a.smask.b + (long long)j * a.smask.c;
-              if (MASKMODE == MASK_MIN) m = reinterpret_cast<const unsigned char*>(a.mask)[mi] ? FLT_MAX : -FLT_MAX;
-              else if (a.mask_kind == EVOATTN_MASK_ADD_F32) m = reinterpret_cast<const float*>(a.mask)[mi];
-              else m = to_float<T>(reinterpret_cast<const T*>(a.mask)[mi]);
-            }
-            dst[j] = m;
+          // eight loads in flight per lane: a dependent load-convert-store chain per key would
+          // make this warp the slowest stage of the pipeline
+          for (int j0 = 0; j0 < r_pad; j0 += 256) {
+            float m[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) m[u] = mask_value<T, MASKMODE == MASK_MIN>(a, it.b, s, j0 + u * 32 + lane);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (j0 + u * 32 + lane < r_pad) dst[j0 + u * 32 + lane] = m[u];
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(m_full(w, st));

@@ -20,4 +20,7 @@ size_t sm100_bwd_workspace_bytes(int dtype, const Args& a);
 int launch_sm100_bwd(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
                      int* launches);
 
+// d(pair_bias) as a kernel of its own (dbias_sm100.cu): needs a.delta filled, writes a.dbias in full.
+int launch_sm100_dbias(int dtype, const Args& a, cudaStream_t st, int* launches);
+
 }  // namespace evo

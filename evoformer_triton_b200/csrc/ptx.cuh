@@ -40,6 +40,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test with a suspend-time hint: the hardware parks the thread until the phase completes
+// or the hint (nanoseconds, capped by the system) runs out, so a waiting warp does not compete
+// for issue slots with the warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(1000000u)
+      : "memory");
+  return ok != 0;
+}
+
 // About one second at B200 clocks.
 constexpr long long kWaitLimitCycles = 2000000000LL;
 
@@ -50,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_parked(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = 1;

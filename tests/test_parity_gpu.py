@@ -247,3 +247,24 @@ def test_reference_shape_matrix(shape, dtype):
     evo.check_device_status()
     for name, got, want in zip(NAMES, (out, q.grad, k.grad, v.grad, b.grad), ref):
         assert reference_allclose(got, want, dtype), f"{name} fails the reference's allclose at {shape}"
+
+
+def test_split_dbias_kernel_matches(monkeypatch):
+    """The stand-alone d(pair_bias) kernel (opt-in with EVOATTN_SPLIT_DBIAS=1) against the oracle.
+    The switch is read once per process, so the check runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import sys, torch; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+        "from test_parity_gpu import rand_inputs, run_op, check\n"
+        "for cfg in [(1, 5, 384, 2, 32, torch.bfloat16), (1, 9, 200, 2, 64, torch.float16), (2, 3, 136, 2, 16, torch.bfloat16)]:\n"
+        "    x = rand_inputs(*cfg, seed=17)\n"
+        "    got, paths = run_op(x)\n"
+        "    assert paths == (2, 2), paths\n"
+        "    check(got, x, label='split-dbias %%s ' %% (cfg,))\n"
+        "print('SPLIT-OK')\n") % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                 os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, EVOATTN_SPLIT_DBIAS="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert "SPLIT-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
