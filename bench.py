@@ -30,6 +30,9 @@ from evoformer_triton_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
 
 METRIC = "evoformer_attn_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
+# profiles/fwd_kernel_C2.md and profiles/bwd_kernel_C2.md (workload C2 only).
+NCU_DRAM_BYTES = {"C2": {"forward kernel": 80378112 + 11543808, "backward call": 163801088 + 62481152}}
 
 
 def measured_peaks():
@@ -135,6 +138,17 @@ def run_reference(args, rank, world):
 
 def dtype_name(dt):
     return {"bfloat16": "bf16", "float16": "fp16", "float32": "fp32"}[str(dt).split(".")[-1]]
+
+
+def algorithmic_bytes(w, backward: bool) -> int:
+    """Bytes one call has to move: forward reads Q,K,V,bias,mask and writes O,LSE; backward reads
+    Q,K,V,O,dO,LSE,bias,mask and writes dQ,dK,dV,dBias (bias and dBias fp32, counted once)."""
+    es = 4 if w.dtype == torch.float32 else 2
+    t = w.B * w.H * w.S * w.R * w.D * es
+    lse = w.B * w.H * w.S * w.R * 4
+    bias = w.B * w.H * w.R * w.R * 4
+    mask = w.B * w.S * w.R
+    return (8 * t + lse + 2 * bias + mask) if backward else (4 * t + lse + bias + mask)
 
 
 def describe(w):
@@ -257,7 +271,10 @@ def main():
         "bound": "tensor", "kernel": "backward call" if dom_bwd else "forward kernel",
         "launches_in_call": bwd_launches if dom_bwd else attention.launches["fwd"],
         "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-        "peak_source": peaks["source"] + " (burst cuBLAS bf16)", "traffic": None,
+        "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+        "traffic": NCU_DRAM_BYTES.get(w.name, {}).get("backward call" if dom_bwd else "forward kernel"),
+        "traffic_unit": "bytes per launch (ncu DRAM read+write of the dominant kernel)",
+        "algorithmic_bytes": algorithmic_bytes(w, backward=dom_bwd),
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "fwd_tflops": w.flops_fwd / (fwd_ms * 1e-3) / 1e12,
         "bwd_tflops": (w.flops_fwd_bwd - w.flops_fwd) / (bwd_ms * 1e-3) / 1e12,
