@@ -51,7 +51,9 @@ def import_reference_attention(ref_dir: str):
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/dsevoformer-triton"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference/dsevoformer-triton")
+    ref_dir = sys.argv[1]
     ref_attention = import_reference_attention(ref_dir)
     for idx, (name, B, H, S, R, D, dtype, mkind) in enumerate(CASES):
         g = torch.Generator().manual_seed(1234 + idx)
