@@ -381,19 +381,36 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
           F2 ls4[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) ls4[u] = f2_make(0.f, 0.f);
+          // Software pipeline over groups of eight keys: the FMAs of group g+1 and the sum / pack of
+          // group g-1 are placed around the eight ex2 of group g, so the results of the
+          // exponential unit are not needed until a group later.
+          float y[8], p[8], pp[8];
+#pragma unroll
+          for (int u = 0; u < 8; u += 2) f2_get(f2_fma(f2_make(x[u], x[u + 1]), l2e2, nm22), y[u], y[u + 1]);
 #pragma unroll
           for (int g8 = 0; g8 < BN / 8; ++g8) {
-            float y[8], p[8];
+            float yn[8];
+            if (g8 + 1 < BN / 8) {
 #pragma unroll
-            for (int u = 0; u < 8; u += 2)
-              f2_get(f2_fma(f2_make(x[g8 * 8 + u], x[g8 * 8 + u + 1]), l2e2, nm22), y[u], y[u + 1]);
+              for (int u = 0; u < 8; u += 2)
+                f2_get(f2_fma(f2_make(x[(g8 + 1) * 8 + u], x[(g8 + 1) * 8 + u + 1]), l2e2, nm22), yn[u], yn[u + 1]);
+            }
 #pragma unroll
             for (int u = 0; u < 8; ++u) p[u] = ex2(y[u]);
+            if (g8 > 0) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              ls4[u] = f2_add(ls4[u], f2_make(p[2 * u], p[2 * u + 1]));
-              pk[g8 * 4 + u] = Pack2<T>::pack(p[2 * u], p[2 * u + 1]);
+              for (int u = 0; u < 4; ++u) {
+                ls4[u] = f2_add(ls4[u], f2_make(pp[2 * u], pp[2 * u + 1]));
+                pk[(g8 - 1) * 4 + u] = Pack2<T>::pack(pp[2 * u], pp[2 * u + 1]);
+              }
             }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { pp[u] = p[u]; y[u] = yn[u]; }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            ls4[u] = f2_add(ls4[u], f2_make(pp[2 * u], pp[2 * u + 1]));
+            pk[(BN / 8 - 1) * 4 + u] = Pack2<T>::pack(pp[2 * u], pp[2 * u + 1]);
           }
           float lsa[8];
 #pragma unroll
