@@ -82,6 +82,7 @@ evo_dbias_kernel(const Args a, const int rows_per_cta, const __grid_constant__ C
   uint64_t* bar_bias = bars + 20;     // resident bias tile landed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 22);
+  volatile uint32_t* scratch = reinterpret_cast<volatile uint32_t*>(bars + 23);  // written, never read
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NT = (a.R + BT - 1) / BT;
@@ -258,6 +259,15 @@ evo_dbias_kernel(const Args a, const int rows_per_cta, const __grid_constant__ C
             }
           }
         }
+      }
+      // The mask stage is handed back only after the loads from it have returned: the store needs
+      // a sum that every one of them fed (an mbarrier arrival by itself does not wait for shared
+      // loads that are still queued).
+      {
+        uint32_t dep = 0;
+#pragma unroll
+        for (int e = 0; e < 64; e += 4) dep ^= __float_as_uint(bacc[e]);
+        *scratch = dep;
       }
       tc_fence_before();
       __syncwarp();

@@ -132,6 +132,7 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
   auto b_empty = [&](int st) { return bars + 2 * PER + BST + st; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + C::kNumBars + 1);
+  volatile uint32_t* scratch = reinterpret_cast<volatile uint32_t*>(bars + C::kNumBars + 2);  // written, never read
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NQT = (a.R + BM - 1) / BM;
@@ -366,6 +367,10 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         }
         const float mx = fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3]));
         if (has_bias) {
+          // The stage is handed back only after the bias loads above have returned: the store needs
+          // the row maximum, which needs every one of them (an mbarrier arrival by itself does not
+          // wait for shared loads that are still queued).
+          *scratch = __float_as_uint(mx);
           __syncwarp();
           if (lane == 0) mbar_arrive(b_empty(g % BST));  // one arrival per warp
         }
