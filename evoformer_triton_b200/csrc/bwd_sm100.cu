@@ -1038,6 +1038,16 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 // but adds almost nothing to global memory.  On B200 the fused form measures faster for every
 // benchmark configuration (the recomputation costs more than the reductions), so the separate
 // kernel is opt-in: EVOATTN_SPLIT_DBIAS=1.
+// Head dimension 32 has two fused kernels: sixteen compute warps (bwd16_sm100.cu, the default:
+// it measures faster on B200) or eight (this file).  EVOATTN_BWD_WARPS=8 picks the latter.
+bool use_sixteen_warps() {
+  static const bool sixteen = [] {
+    const char* e = getenv("EVOATTN_BWD_WARPS");
+    return !(e && e[0] == '8');
+  }();
+  return sixteen;
+}
+
 bool split_dbias(const Args& a) {
   static const bool want_split = [] {
     const char* e = getenv("EVOATTN_SPLIT_DBIAS");
@@ -1070,7 +1080,8 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
     if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, DP <= 32 ? 16 : 32)) return EVOATTN_ERR_CUDA;
     const Str3 dense{(long long)a.H * a.R * a.R, (long long)a.R * a.R, (long long)a.R};
     if (!a.dbias) tdb = tq;  // d_bias comes from the separate kernel
-    else if (!make_bias_map(&tdb, a.dbias, dense, a.B, a.H, a.R, BT, 32)) return EVOATTN_ERR_CUDA;
+    else if (!make_bias_map(&tdb, a.dbias, dense, a.B, a.H, a.R, BT, (DP == 32 && use_sixteen_warps()) ? 16 : 32))
+      return EVOATTN_ERR_CUDA;  // the sixteen-warp kernel reduces 128x16 blocks, the others 128x32
   } else {
     tb = tq;
     tdb = tq;
@@ -1099,10 +1110,16 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       return EVOATTN_ERR_CUDA;
     const long long ctas = items < sms ? items : sms;
-    auto kern = add ? evo_bwd_ws_kernel<T, DP, MASK_ADD> : evo_bwd_ws_kernel<T, DP, MASK_MIN>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)W::bytes) != cudaSuccess)
-      return EVOATTN_ERR_CUDA;
-    kern<<<(unsigned)ctas, 384, W::bytes, st>>>(a, dq_acc, (int)items, tq, tk, tv, tdo, tb, tdb);
+    if (DP == 32 && use_sixteen_warps()) {
+      const int rc = launch_sm100_bwd16(std::is_same<T, __nv_bfloat16>::value ? EVOATTN_BF16 : EVOATTN_FP16, a, dq_acc,
+                                        items, (int)ctas, tq, tk, tv, tdo, tb, tdb, st);
+      if (rc != EVOATTN_OK) return rc;
+    } else {
+      auto kern = add ? evo_bwd_ws_kernel<T, DP, MASK_ADD> : evo_bwd_ws_kernel<T, DP, MASK_MIN>;
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)W::bytes) != cudaSuccess)
+        return EVOATTN_ERR_CUDA;
+      kern<<<(unsigned)ctas, 384, W::bytes, st>>>(a, dq_acc, (int)items, tq, tk, tv, tdo, tb, tdb);
+    }
   } else {
     const long long ctas = (long long)a.B * a.H * NT * ((a.S + G - 1) / G);
     auto kern = add ? evo_bwd_sm100_kernel<T, DP, MASK_ADD> : evo_bwd_sm100_kernel<T, DP, MASK_MIN>;

@@ -1,5 +1,6 @@
 // Host-side launch entry points of the kernel families (internal to the library).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 
@@ -19,6 +20,13 @@ bool sm100_bwd_supported(int dtype, const Args& a);
 size_t sm100_bwd_workspace_bytes(int dtype, const Args& a);
 int launch_sm100_bwd(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
                      int* launches);
+
+// The fused backward kernel with sixteen compute warps (bwd16_sm100.cu; head dimension padded to
+// 32): work list of `items` items on `ctas` persistent CTAs, tensor maps as built by
+// launch_sm100_bwd for its own kernel.
+int launch_sm100_bwd16(int dtype, const Args& a, float* dq_acc, long long items, int ctas, const CUtensorMap& tq,
+                       const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tb,
+                       const CUtensorMap& tdb, cudaStream_t st);
 
 // d(pair_bias) as a kernel of its own (dbias_sm100.cu): needs a.delta filled, writes a.dbias in full.
 int launch_sm100_dbias(int dtype, const Args& a, cudaStream_t st, int* launches);

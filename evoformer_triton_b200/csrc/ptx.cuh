@@ -103,6 +103,12 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const 
       ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tma_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until the bulk groups of this thread have finished READING their shared-memory source.
 __device__ __forceinline__ void tma_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
@@ -244,6 +250,36 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 #undef EVO_I4
+
+// ---------------------------------------------------------------- predicated global loads
+// A load whose value is needed much later must not be followed by a select on its result: the
+// select would wait for the load where it stands.  These write the destination only when `pred`
+// holds and leave `dflt` in it otherwise; the address is not touched when `pred` is false.
+__device__ __forceinline__ float ldg_f32_if(const float* p, bool pred, float dflt) {
+  float v = dflt;
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q ld.global.f32 %0, [%1];\n\t}"
+               : "+f"(v) : "l"(p), "r"((int)pred));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_u32_if(const void* p, bool pred) {
+  uint32_t v = 0u;
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q ld.global.u32 %0, [%1];\n\t}"
+               : "+r"(v) : "l"(p), "r"((int)pred));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_u16_if(const void* p, bool pred) {
+  uint32_t v = 0u;
+  asm volatile("{\n\t.reg .pred q;\n\t.reg .b16 h;\n\tsetp.ne.b32 q, %2, 0;\n\tmov.b16 h, 0;\n\t"
+               "@q ld.global.u16 h, [%1];\n\t@q cvt.u32.u16 %0, h;\n\t}"
+               : "+r"(v) : "l"(p), "r"((int)pred));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_u8_if(const void* p, bool pred) {
+  uint32_t v = 0u;
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q ld.global.u8 %0, [%1];\n\t}"
+               : "+r"(v) : "l"(p), "r"((int)pred));
+  return v;
+}
 
 // ---------------------------------------------------------------- small math / sync helpers
 __device__ __forceinline__ float ex2(float x) {

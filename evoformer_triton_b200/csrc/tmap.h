@@ -19,4 +19,8 @@ bool make_qkv_map(CUtensorMap* out, const void* base, const Str4& stride_elems, 
 bool make_bias_map(CUtensorMap* out, const float* base, const Str3& stride_elems, int B, int H, int R, int box_i,
                    int box_j);
 
+// Contiguous fp32 [slabs, R, D] (the dQ accumulator: one slab per (b,h,s)) as a 3-D map
+// (D, R, slabs) with box (box_d, box_r, 1); rows and columns beyond R and D are clipped.
+bool make_rows_f32_map(CUtensorMap* out, const float* base, int D, int R, long long slabs, int box_d, int box_r);
+
 }  // namespace evo
