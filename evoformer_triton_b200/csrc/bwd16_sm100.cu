@@ -48,15 +48,15 @@ constexpr int kComputeWarps = 16;
 struct Smem16 {
   static constexpr int kTile = BT * RB;                   // one Q, dO, K or V tile
   static constexpr int kPS = BT * BT * 2;                 // the P or the dS tile
-  static constexpr int kBiasChunk = BT * 64;              // 128 rows x 16 fp32, 64-byte swizzle
+  static constexpr int kBiasBlock = BT * 128;             // 128 rows x 32 fp32, 128-byte swizzle
   static constexpr int kStage = 4 * kTile;                // Q, dO, K, V of one step
   static constexpr int kStages = 2;
   static constexpr int offStage = 0;
   static constexpr int offP = offStage + kStages * kStage;
   static constexpr int offDS = offP + kPS;
-  static constexpr int offB = offDS + kPS;                // [4 column quarters][2 chunks]
+  static constexpr int offB = offDS + kPS;                // one block per column quarter
   static constexpr int kDQ = BT * DP * 4;                 // a dQ partial: 128 rows x 32 fp32, 128-byte swizzle
-  static constexpr int offDQ = offB + 8 * kBiasChunk;     // 2 buffers
+  static constexpr int offDQ = offB + 4 * kBiasBlock;     // 2 buffers
   static constexpr int offMask = offDQ + 2 * kDQ;         // G x 128 floats
   static constexpr int offBars = offMask + G * BT * 4;
   static constexpr size_t bytes = offBars + 256 + 1024;
@@ -117,8 +117,8 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
   uint64_t* bar_ld = bars + 0;       // [3] tiles of a step landed
   uint64_t* bar_sdp = bars + 3;      // S, dP of a step complete
   uint64_t* bar_out = bars + 4;      // dV, dK, dQ MMAs of a step complete
-  uint64_t* bar_bfull = bars + 5;    // [4 quarters][2] that pair-bias chunk landed
-  uint64_t* bar_bempty = bars + 13;  // [4 quarters][2] ... may be refilled (one arrival per warp): it has been read,
+  uint64_t* bar_bfull = bars + 5;    // [4 quarters] that quarter's pair-bias block (32 key columns) landed
+  uint64_t* bar_bempty = bars + 13;  // [4 quarters] ... may be refilled (one arrival per warp): it has been read,
                                      // or, after a row group's last step, holds the quarter's d_bias values instead
   uint64_t* bar_sread = bars + 21;   // the 16 compute warps hold their S, dP columns of a step in registers
   uint64_t* bar_cdone = bars + 22;   // the 16 compute warps finished a step (P, dS written; dQ read)
@@ -180,7 +180,7 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
     mbar_init(bar_out, 1);
     mbar_init(bar_cdone, kComputeWarps);  // one arrival per compute warp
     mbar_init(bar_sread, kComputeWarps);
-    for (int i = 0; i < 8; ++i) { mbar_init(bar_bfull + i, 1); mbar_init(bar_bempty + i, 4); }
+    for (int i = 0; i < 4; ++i) { mbar_init(bar_bfull + i, 1); mbar_init(bar_bempty + i, 4); }
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
     if (has_bias) prefetch_tmap(&tmB);
@@ -319,43 +319,35 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
       }
     } else if (warp <= kComputeWarps + 2 && has_bias) {
       // ====== pair-bias loaders: warp 17 feeds column quarters 0 and 1, warp 18 quarters 2 and 3 ======
-      // A quarter has two chunk buffers (16 key columns each), filled once per step, a whole step
-      // ahead.  After the last step of a row group the compute warps hand a buffer back holding the
-      // quarter's d_bias values for those 16 columns instead of the bias they read from it: this
-      // warp then adds them to d_bias in global memory with a bulk tensor reduction and refills
-      // the buffer once the reduction has read it.
+      // A quarter's buffer holds the bias of its 32 key columns for one step (rows of 128 bytes:
+      // half as many rows for the copy engine as two 16-column chunks would be) and is refilled
+      // as soon as the quarter's warps have read it, most of a step before it is needed again.
+      // After the last step of a row group the compute warps hand the buffer back holding the
+      // quarter's d_bias block instead of the bias they read from it: this warp then adds it to
+      // d_bias in global memory with a bulk tensor reduction and refills the buffer once the
+      // reduction has read it.
       const int q0 = (warp - kComputeWarps - 1) * 2;
       StepId16 pd = decode(0);
       bool prev_flush = false;
       for (int n = 0; n <= total_steps; ++n) {
         const bool load = n < total_steps;
-        const StepId16 d = decode(load ? n : 0);
         if (!load && !prev_flush) break;
-        for (int sub = 0; sub < 2; ++sub) {
+        const StepId16 d = decode(load ? n : 0);
 #pragma unroll
-          for (int qq = 0; qq < 2; ++qq) {
-            const int buf = (q0 + qq) * 2 + sub;
-            mbar_wait(bar_bempty + buf, (n & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
-            if (prev_flush && lane == 0)
-              tma_reduce_add_4d(&tmDB, sB + buf * L::kBiasChunk, pd.j0 + (q0 + qq) * 32 + sub * 16, pd.it * BT, pd.h, pd.b);
-          }
+        for (int qq = 0; qq < 2; ++qq) {
+          const int qd = q0 + qq;
+          mbar_wait(bar_bempty + qd, (n & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
           if (prev_flush && lane == 0) {
+            tma_reduce_add_4d(&tmDB, sB + qd * L::kBiasBlock, pd.j0 + qd * 32, pd.it * BT, pd.h, pd.b);
             tma_commit_group();
             if (load) tma_wait_group_read0(); else tma_wait_group0();
           }
           __syncwarp();
-          if (load) {
-#pragma unroll
-            for (int qq = 0; qq < 2; ++qq) {
-              const int buf = (q0 + qq) * 2 + sub;
-              if (lane == 0) {
-                mbar_expect_tx(bar_bfull + buf, L::kBiasChunk);
-                tma_load_4d(sB + buf * L::kBiasChunk, &tmB, bar_bfull + buf, d.j0 + (q0 + qq) * 32 + sub * 16, d.it * BT, d.h,
-                            d.b);
-              }
-            }
-            __syncwarp();
+          if (load && lane == 0) {
+            mbar_expect_tx(bar_bfull + qd, L::kBiasBlock);
+            tma_load_4d(sB + qd * L::kBiasBlock, &tmB, bar_bfull + qd, d.j0 + qd * 32, d.it * BT, d.h, d.b);
           }
+          __syncwarp();
         }
         prev_flush = load && (d.g == G - 1) && (a.dbias != nullptr);
         pd = d;
@@ -476,24 +468,24 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
         uint32_t sr[16], dr[16];
         tmem_ld16(t_lane + colS + col0, sr);
         tmem_ld16(t_lane + colDP + col0, dr);
-        // pair bias: my row's 16 floats (64 bytes, 64-byte swizzle)
+        // pair bias: 16 of my row's 32 floats (rows of 128 bytes, 128-byte swizzle)
         float bv[16];
-        uint8_t* brow = sB + (qd * 2 + sub) * L::kBiasChunk + row * 64;
+        uint8_t* brow = sB + qd * L::kBiasBlock + row * 128;
         if (has_bias) {
-          mbar_wait(bar_bfull + qd * 2 + sub, step & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+          if (sub == 0) mbar_wait(bar_bfull + qd, step & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
-            const float4 f = *reinterpret_cast<const float4*>(brow + ((q4 ^ ((row >> 1) & 3)) << 4));
+            const float4 f = *reinterpret_cast<const float4*>(brow + (((sub * 4 + q4) ^ (row & 7)) << 4));
             bv[q4 * 4 + 0] = f.x; bv[q4 * 4 + 1] = f.y; bv[q4 * 4 + 2] = f.z; bv[q4 * 4 + 3] = f.w;
           }
-          if (!flush) {
-            // The buffer is handed back only after the loads above have returned: a store that
-            // needs one word of each of them is issued first (an mbarrier arrival does not wait
-            // for shared loads still queued behind this warp's global reductions, and the refill
-            // would then overwrite what they are about to read).
+          if (!flush && sub == 1) {
+            // The buffer is handed back only after the loads from it have returned: a store that
+            // needs one word of each of this block's loads is issued first, and the first block's
+            // values have been used by then (an mbarrier arrival does not wait for shared loads
+            // still queued, and the refill would overwrite what they are about to read).
             *scratch = __float_as_uint(bv[0]) ^ __float_as_uint(bv[4]) ^ __float_as_uint(bv[8]) ^ __float_as_uint(bv[12]);
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_bempty + qd * 2 + sub);  // one arrival per warp
+            if (lane == 0) mbar_arrive(bar_bempty + qd);  // one arrival per warp
           }
         } else {
 #pragma unroll
@@ -534,17 +526,19 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
           }
         }
         if (flush && has_bias) {
-          // These 16 columns of the quarter's d_bias block are final: they go where the bias chunk
-          // was (same rows, same swizzle), and the buffer goes back to the loader warp, which adds
-          // it to d_bias in global memory before it refills it.
+          // These 16 columns of the quarter's d_bias block are final: they go where their bias
+          // values were (same rows, same swizzle); after the second block the buffer goes back to
+          // the loader warp, which adds it to d_bias in global memory before it refills it.
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4)
-            *reinterpret_cast<float4*>(brow + ((q4 ^ ((row >> 1) & 3)) << 4)) =
+            *reinterpret_cast<float4*>(brow + (((sub * 4 + q4) ^ (row & 7)) << 4)) =
                 make_float4(bacc[sub * 16 + q4 * 4], bacc[sub * 16 + q4 * 4 + 1], bacc[sub * 16 + q4 * 4 + 2],
                             bacc[sub * 16 + q4 * 4 + 3]);
-          fence_async_shared();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_bempty + qd * 2 + sub);
+          if (sub == 1) {
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_bempty + qd);
+          }
         }
         if (!out_seen) {
           // P and dS have one buffer each: the previous step's dV/dK/dQ MMAs must have read them.

@@ -801,14 +801,12 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, c
     // huge lse so that their P is exactly 0)
     float lse_next = 1e30f, delta_next = 0.f;
     auto load_row_stats = [&](const StepId& d, bool in_range) {
-      lse_next = 1e30f;
-      delta_next = 0.f;
+      // predicated loads: a select on the loaded value would wait for the load right here
       const int i = d.it * BT + row;
-      if (in_range && i < a.R && d.s < a.S) {
-        const long long ri = (((long long)d.b * a.H + d.h) * a.S + d.s) * a.R + i;
-        lse_next = a.lse[ri];
-        delta_next = a.delta[ri];
-      }
+      const bool ok = in_range && i < a.R && d.s < a.S;
+      const long long ri = (((long long)d.b * a.H + d.h) * a.S + d.s) * a.R + i;
+      lse_next = ldg_f32_if(a.lse + ri, ok, 1e30f);
+      delta_next = ldg_f32_if(a.delta + ri, ok, 0.f);
     };
     // The compute warps step their position instead of decoding it: the divisions of `decode` are a
     // dependent chain of several hundred cycles, paid only when an item ends.
@@ -1077,11 +1075,12 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (!make_qkv_map(&tdo, a.d_o, a.sdo, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   CUtensorMap tdb;
   if (a.bias) {
-    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, DP <= 32 ? 16 : 32)) return EVOATTN_ERR_CUDA;
+    // 128x16 chunks for the eight-warp kernel, 128x32 blocks for the others
+    const bool sixteen = (DP == 32 && use_sixteen_warps());
+    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, (DP <= 32 && !sixteen) ? 16 : 32)) return EVOATTN_ERR_CUDA;
     const Str3 dense{(long long)a.H * a.R * a.R, (long long)a.R * a.R, (long long)a.R};
     if (!a.dbias) tdb = tq;  // d_bias comes from the separate kernel
-    else if (!make_bias_map(&tdb, a.dbias, dense, a.B, a.H, a.R, BT, (DP == 32 && use_sixteen_warps()) ? 16 : 32))
-      return EVOATTN_ERR_CUDA;  // the sixteen-warp kernel reduces 128x16 blocks, the others 128x32
+    else if (!make_bias_map(&tdb, a.dbias, dense, a.B, a.H, a.R, BT, 32)) return EVOATTN_ERR_CUDA;
   } else {
     tb = tq;
     tdb = tq;
