@@ -32,7 +32,7 @@ METRIC = "evoformer_attn_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
 # profiles/fwd_kernel_C2.md and profiles/bwd_kernel_C2.md (workload C2 only).
-NCU_DRAM_BYTES = {"C2": {"forward kernel": 80378112 + 11543808, "backward call": 163801088 + 62481152}}
+NCU_DRAM_BYTES = {"C2": {"forward kernel": 80339200 + 8521216, "backward call": 163806208 + 58541824}}
 
 
 def measured_peaks():
