@@ -129,6 +129,9 @@ SHAPES = [
     (1, 1, 640, 1, 64, torch.bfloat16, "none", False),
     (1, 2, 96, 2, 24, torch.bfloat16, "bool", True),       # D not a power of two
     (1, 2, 50, 2, 32, torch.bfloat16, "bool", True),       # R % 4 != 0: CUDA-core path
+    (1, 4, 200, 2, 32, torch.bfloat16, "add32", True),     # additive masks at D=32 (sixteen-warp backward)
+    (1, 5, 136, 2, 32, torch.float16, "addsame", True),
+    (1, 7, 384, 3, 24, torch.bfloat16, "add32", False),    # D < 32 padded, no pair bias, ragged row group
 ]
 
 
@@ -283,3 +286,26 @@ def test_split_dbias_kernel_matches(monkeypatch):
     env = dict(os.environ, EVOATTN_SPLIT_DBIAS="1")
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
     assert "SPLIT-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_eight_warp_backward_matches():
+    """Head dimension 32 runs the sixteen-warp fused backward by default; EVOATTN_BWD_WARPS=8
+    selects the eight-warp kernel (the one D <= 16 always uses).  The switch is read once per
+    process, so the check runs in a child process; it includes a case with several work items per
+    persistent CTA and a ragged last row group."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import sys, torch; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+        "from test_parity_gpu import rand_inputs, run_op, check\n"
+        "for cfg in [(1, 5, 384, 2, 32, torch.bfloat16), (1, 64, 200, 8, 24, torch.float16), (2, 7, 136, 2, 32, torch.bfloat16)]:\n"
+        "    x = rand_inputs(*cfg, seed=23)\n"
+        "    got, paths = run_op(x)\n"
+        "    assert paths == (2, 2), paths\n"
+        "    check(got, x, label='eight-warp %%s ' %% (cfg,))\n"
+        "print('EIGHT-OK')\n") % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                 os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, EVOATTN_BWD_WARPS="8")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert "EIGHT-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
