@@ -410,10 +410,14 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
     // log-sum-exp and delta of this thread's query row for a step (rows that do not exist get a
     // huge lse so that their P is exactly 0)
     float lse_next = 1e30f, delta_next = 0.f;
+    // `slab` = index of the [R] row of (b, h, row-group start) in the [B,H,S,R] statistics: the
+    // 64-bit index arithmetic is done once per item, a step adds small offsets to it
+    long long slab = 0;
+    auto set_slab = [&](const StepId16& d) { slab = (((long long)d.b * a.H + d.h) * a.S + (d.s - d.g)) * a.R; };
     auto load_row_stats = [&](const StepId16& d, bool in_range) {
       const int i = d.it * BT + row;
       const bool ok = in_range && i < a.R && d.s < a.S;
-      const long long ri = (((long long)d.b * a.H + d.h) * a.S + d.s) * a.R + i;
+      const long long ri = slab + d.g * a.R + i;
       lse_next = ldg_f32_if(a.lse + ri, ok, 1e30f);
       delta_next = ldg_f32_if(a.delta + ri, ok, 0.f);
     };
@@ -429,6 +433,7 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
       d.s = c.s - c.g + d.g;
       return d;
     };
+    set_slab(cur);
     load_row_stats(cur, total_steps > 0);
     int pb = 0, ph = 0, ps0 = 0, pj0 = 0;     // the item whose dK/dV still sit in TMEM
     float bacc[32];
@@ -449,9 +454,13 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
       // placed after the new load would wait for the new one as well.
       float lse = lse_next, delta = delta_next;
       asm volatile("" : "+f"(lse), "+f"(delta)::"memory");
-      load_row_stats(nxt, more);  // in flight during this step
       // the next item's residue mask, fetched under this item's last step (G*128 = 384 values)
-      const uint32_t mnext = mask_fetch(nxt.b, nxt.s + tid / BT, nxt.j0 + (tid % BT), item_ends && more && tid < G * BT);
+      uint32_t mnext = 0u;
+      if (item_ends) {  // warp-uniform: the index arithmetic is skipped on the other steps
+        set_slab(nxt);
+        mnext = mask_fetch(nxt.b, nxt.s + tid / BT, nxt.j0 + (tid % BT), more && tid < G * BT);
+      }
+      load_row_stats(nxt, more);  // in flight during this step
       const bool dead = (lse == -FLT_MAX);  // every key of this row was dropped: P is uniform
       const float nlse = -lse * kLog2e;
       const F2 nlse2 = f2_make(nlse, nlse), delta2 = f2_make(delta, delta);
