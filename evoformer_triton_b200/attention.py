@@ -8,8 +8,10 @@ work is done by libevoattn.so through its C ABI; torch is used for memory and st
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 import os
+import threading
 from typing import Optional, Sequence
 
 import torch
@@ -153,6 +155,23 @@ def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o):
     return dq, dk, dv, dbias
 
 
+_pending = threading.local()
+
+
+@contextlib.contextmanager
+def pair_bias_grad_summed_over(group):
+    """Calls of the op made inside this context sum their d(pair_bias) over the ranks of
+    ``group`` (``None`` = the default process group) in backward: the fp32 sum over the local
+    MSA rows is all-reduced as it leaves the kernel, before the single cast to the bias dtype.
+    Used by :func:`evoformer_triton_b200.sharding.sharded_evoformer_attention`."""
+    prev = getattr(_pending, "group", None)
+    _pending.group = (group,)
+    try:
+        yield
+    finally:
+        _pending.group = prev
+
+
 class _EvoformerAttentionBase(torch.autograd.Function):
     """Shared implementation; ``layout`` is fixed by the two public subclasses."""
 
@@ -187,6 +206,7 @@ class _EvoformerAttentionBase(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, mask, bias, o, lse)  # evoformer.py:729
         ctx.softmax_scale = scale
         ctx.bias_meta = None if pair_bias is None else (pair_bias.dtype, tuple(pair_bias.shape))
+        ctx.reduce_group = getattr(_pending, "group", None)
         return _unview(o, cls.layout)
 
     @classmethod
@@ -201,6 +221,9 @@ class _EvoformerAttentionBase(torch.autograd.Function):
         d_pair_bias = None
         if dbias is not None:
             dtype, shape = ctx.bias_meta
+            if ctx.reduce_group is not None:  # N_seq is sharded: the other ranks' rows belong to the sum
+                import torch.distributed as dist
+                dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=ctx.reduce_group[0])
             # the sum over N_seq stays in fp32 until this single cast (evoformer.py:860 casts to dO's dtype)
             d_pair_bias = dbias.reshape(shape).to(dtype)
         return _unview(dq, cls.layout), _unview(dk, cls.layout), _unview(dv, cls.layout), None, d_pair_bias

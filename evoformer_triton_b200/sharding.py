@@ -84,5 +84,13 @@ def sharded_evoformer_attention(attn_fn, Q, K, V, res_mask, pair_bias, group=Non
     no communication; backward all-reduces d(pair_bias).
     """
     if pair_bias is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+        owner = getattr(attn_fn, "__self__", None)
+        from . import attention
+        if isinstance(owner, type) and issubclass(owner, attention._EvoformerAttentionBase):
+            # this package's op: its backward all-reduces the fp32 d(pair_bias) as it leaves the
+            # kernel, before the cast to the bias dtype (one collective, no extra conversions, and
+            # the local partial sums are never rounded to 16 bits)
+            with attention.pair_bias_grad_summed_over(group):
+                return attn_fn(Q, K, V, res_mask, pair_bias)
         pair_bias = replicate_pair_bias(pair_bias, group)
     return attn_fn(Q, K, V, res_mask, pair_bias)
