@@ -4,8 +4,9 @@
 // Replaces dsevoformer-triton/evoformer.py:479-630 (_attn_bwd_dk_dv) and :329-476 (_attn_bwd_dq);
 // the decomposition into work items and steps, the TMEM budget and the shared-memory layout are
 // those of the warp-specialised kernel in bwd_sm100.cu.  What differs is who does the arithmetic:
-//   * 640 threads: warps 0-15 compute, warp 16 issues the Q/dO/K/V loads and every tcgen05.mma,
-//     warps 17 and 18 feed the pair bias, warp 19 idles.
+//   * 640 threads: warps 0-15 compute, warp 16 issues every tcgen05.mma and the dQ reductions,
+//     warps 17 and 18 feed the pair bias and send the d_bias blocks off, warp 19 loads the
+//     Q/dO/K/V tiles.
 //   * Compute warp w owns query rows 32*(w%4).. (the TMEM lanes a warp may read) and the 32 key
 //     columns of quarter w/4.  A step of the eight-warp kernel is a serial chain of waits, loads,
 //     arithmetic and stores per warp with two warps per scheduler; here each chain is half as
@@ -42,9 +43,9 @@ constexpr int kComputeWarps = 16;
 
 // Shared memory.  P and dS have one buffer each: the dV/dK/dQ MMAs of a step are issued the
 // moment its last compute warp is done and have completed before the next step's first P/dS
-// stores (which wait for them anyway).  That leaves room for the pair bias of a whole step (two
-// chunks per column quarter) and for two staging tiles from which the dQ partials leave as bulk
-// tensor reductions.
+// stores (which wait for them anyway).  That leaves room for the pair bias of a whole step (one
+// block of 32 key columns per column quarter) and for two staging tiles from which the dQ partials
+// leave as bulk tensor reductions.  Q, dO, K, V of a step arrive two steps ahead in a two-deep ring.
 struct Smem16 {
   static constexpr int kTile = BT * RB;                   // one Q, dO, K or V tile
   static constexpr int kPS = BT * BT * 2;                 // the P or the dS tile
@@ -114,7 +115,7 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
   uint8_t* sDQ = smem + L::offDQ;
   float* sMask = reinterpret_cast<float*>(smem + L::offMask);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBars);
-  uint64_t* bar_ld = bars + 0;       // [3] tiles of a step landed
+  uint64_t* bar_ld = bars + 0;       // [2] tiles of a step landed
   uint64_t* bar_sdp = bars + 3;      // S, dP of a step complete
   uint64_t* bar_out = bars + 4;      // dV, dK, dQ MMAs of a step complete
   uint64_t* bar_bfull = bars + 5;    // [4 quarters] that quarter's pair-bias block (32 key columns) landed
