@@ -88,11 +88,6 @@ template <int N> __device__ __forceinline__ void setmaxnreg_dec16() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-__device__ __forceinline__ void red_add_v4_16(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
-
 template <class T>
 __global__ void __launch_bounds__(kThreads16, 1)
 evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, const __grid_constant__ CUtensorMap tmQ,
