@@ -60,7 +60,7 @@ struct Cfg {
   static constexpr int offMask = offB + BST * kBias;
   static constexpr int kNumBars = 2 * (2 * QST + 4 * NKV + 2 + 1 + 2 + 4) + 2 * BST;
   static size_t bytes(int r_pad) {
-    return (size_t)offMask + (size_t)4 * r_pad * 4 + kNumBars * 8 + 64 + 1024;
+    return (size_t)offMask + (size_t)4 * r_pad * 4 + 4 * 32 * 4 + kNumBars * 8 + 64 + 1024;
   }
   // TMEM columns of warpgroup w: S double buffer, then PV double buffer
   static constexpr int tmemWg = 2 * BN + 2 * DP;
@@ -114,7 +114,10 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
   const int T_TILES = (a.R + BN - 1) / BN;
   const int r_pad = T_TILES * BN;
   float* sMask = reinterpret_cast<float*>(smem + C::offMask);  // [warpgroup][stage][r_pad]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sMask + 4 * r_pad);
+  // one word per key tile of a staged mask row: non-zero if the tile has a dropped key (a key tile
+  // without one skips the mask arithmetic and the mask loads in the boolean form); R <= 2048
+  uint32_t* sDirty = reinterpret_cast<uint32_t*>(sMask + 4 * r_pad);  // [warpgroup][stage][32]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDirty + 4 * 32);
   // barrier layout: per warpgroup w a block of PER, then the shared bias barriers
   constexpr int PER = 2 * QST + 4 * NKV + 2 + 1 + 2 + 4;
   auto q_full = [&](int w, int st) { return bars + w * PER + st; };
@@ -273,6 +276,9 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
           const int s = min(2 * it.sp + w, a.S - 1);
           mbar_wait(m_empty(w, st), ((n >> 1) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
           float* dst = sMask + (w * 2 + st) * r_pad;
+          uint32_t* dirty = sDirty + (w * 2 + st) * 32;
+          dirty[lane] = 0u;
+          __syncwarp();
           // eight loads in flight per lane: a dependent load-convert-store chain per key would
           // make this warp the slowest stage of the pipeline
           for (int j0 = 0; j0 < r_pad; j0 += 256) {
@@ -280,8 +286,12 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
 #pragma unroll
             for (int u = 0; u < 8; ++u) m[u] = mask_value<T, MASKMODE == MASK_MIN>(a, it.b, s, j0 + u * 32 + lane);
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (j0 + u * 32 + lane < r_pad) dst[j0 + u * 32 + lane] = m[u];
+            for (int u = 0; u < 8; ++u) {
+              const bool in = j0 + u * 32 + lane < r_pad;
+              if (in) dst[j0 + u * 32 + lane] = m[u];
+              const uint32_t any = __ballot_sync(0xffffffffu, in && m[u] < 0.f);
+              if (lane == 0 && any != 0u) dirty[(j0 + u * 32) / BN] = 1u;
+            }
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(m_full(w, st));
@@ -314,6 +324,7 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
       const uint32_t mst = n_item & 1;
       mbar_wait(m_full(w, mst), (n_item >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
       const float* mrow_base = sMask + (w * 2 + mst) * r_pad;
+      const uint32_t* dirty_row = sDirty + (w * 2 + mst) * 32;
 
       float m_run = -FLT_MAX, l_run = 0.f, alpha_pending = 1.f;
       float acc[DP];
@@ -338,33 +349,42 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         tmem_ld32(t_base + (g & 1) * BN, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
         tmem_ld32(t_base + (g & 1) * BN + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
         tmem_wait_ld();
+        // A key tile of a boolean mask without a dropped key needs neither the mask values nor
+        // the `min` (most tiles: masks are mostly trailing padding); the flag is warp-uniform.
+        auto scores = [&](auto with_mask) {
+          constexpr bool kMask = decltype(with_mask)::value;
 #pragma unroll
-        for (int g8 = 0; g8 < BN / 8; ++g8) {
-          const int c = g8 >> 2, q4 = (g8 & 3) * 2;
-          float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
-          if (has_bias) {
-            b0 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + ((q4 ^ (row & 7)) << 4));
-            b1 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + (((q4 + 1) ^ (row & 7)) << 4));
+          for (int g8 = 0; g8 < BN / 8; ++g8) {
+            const int c = g8 >> 2, q4 = (g8 & 3) * 2;
+            float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+            if (has_bias) {
+              b0 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + ((q4 ^ (row & 7)) << 4));
+              b1 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + (((q4 + 1) ^ (row & 7)) << 4));
+            }
+            const float bvv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u += 2) {  // x = scale*S + bias, two elements per instruction
+              const F2 t = f2_fma(f2_from_bits(sr[g8 * 8 + u], sr[g8 * 8 + u + 1]), scale2, f2_make(bvv[u], bvv[u + 1]));
+              f2_get(t, v[u], v[u + 1]);
+            }
+            if constexpr (kMask) {
+              const float4 k0 = *reinterpret_cast<const float4*>(mrow + g8 * 8);
+              const float4 k1 = *reinterpret_cast<const float4*>(mrow + g8 * 8 + 4);
+              const float mkv[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+#pragma unroll
+              for (int u = 0; u < 8; ++u) v[u] = (MASKMODE == MASK_MIN) ? fminf(v[u], mkv[u]) : (v[u] + mkv[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u += 2) {
+              x[g8 * 8 + u] = v[u];
+              x[g8 * 8 + u + 1] = v[u + 1];
+              mx8[u >> 1] = max3(mx8[u >> 1], v[u], v[u + 1]);
+            }
           }
-          const float4 k0 = *reinterpret_cast<const float4*>(mrow + g8 * 8);
-          const float4 k1 = *reinterpret_cast<const float4*>(mrow + g8 * 8 + 4);
-          const float bvv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-          const float mkv[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
-          float v[8];
-#pragma unroll
-          for (int u = 0; u < 8; u += 2) {  // x = scale*S + bias, two elements per instruction
-            const F2 t = f2_fma(f2_from_bits(sr[g8 * 8 + u], sr[g8 * 8 + u + 1]), scale2, f2_make(bvv[u], bvv[u + 1]));
-            f2_get(t, v[u], v[u + 1]);
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) v[u] = (MASKMODE == MASK_MIN) ? fminf(v[u], mkv[u]) : (v[u] + mkv[u]);
-#pragma unroll
-          for (int u = 0; u < 8; u += 2) {
-            x[g8 * 8 + u] = v[u];
-            x[g8 * 8 + u + 1] = v[u + 1];
-            mx8[u >> 1] = max3(mx8[u >> 1], v[u], v[u + 1]);
-          }
-        }
+        };
+        if (MASKMODE != MASK_MIN || dirty_row[t] != 0u) scores(std::true_type{});
+        else scores(std::false_type{});
         const float mx = fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3]));
         if (has_bias) {
           // The stage is handed back only after the bias loads above have returned: the store needs
