@@ -131,14 +131,18 @@ def attention_forward(q, k, v, mask, bias, scale):
     return o, lse
 
 
-def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o):
-    """Raw backward on attention-view tensors.  Returns (dq, dk, dv, dbias fp32 or None)."""
+def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True):
+    """Raw backward on attention-view tensors.  Returns (dq, dk, dv, dbias fp32 or None).
+    ``want_dbias=False`` skips d(pair_bias) (its reductions are the backward's largest stream
+    of writes; speed_benchmark.py:68 builds the bias without ``requires_grad``)."""
     lib = _lib.load()
     B, H, S, R, D = q.shape
     dq = torch.empty((B, H, S, R, D), dtype=q.dtype, device=q.device)
     dk = torch.empty_like(dq)
     dv = torch.empty_like(dq)
-    dbias = None if bias is None else torch.empty((B, H, R, R), dtype=torch.float32, device=q.device)
+    dbias = None
+    if bias is not None and want_dbias:
+        dbias = torch.empty((B, H, R, R), dtype=torch.float32, device=q.device)
     p = _lib.BwdParams()
     _fill_fwd(p.fwd, q, k, v, o, lse, mask, bias, scale)
     p.d_o, p.dq, p.dk, p.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
@@ -217,7 +221,9 @@ class _EvoformerAttentionBase(torch.autograd.Function):
         d_o = _prep_operand(_view_dims(dO, cls.layout))
         if d_o.dtype != q.dtype:
             d_o = d_o.to(q.dtype)
-        dq, dk, dv, dbias = attention_backward(q, k, v, o, lse, mask, bias, ctx.softmax_scale, d_o)
+        want_dbias = bias is not None and ctx.needs_input_grad[4]
+        dq, dk, dv, dbias = attention_backward(q, k, v, o, lse, mask, bias, ctx.softmax_scale, d_o,
+                                               want_dbias=want_dbias)
         d_pair_bias = None
         if dbias is not None:
             dtype, shape = ctx.bias_meta

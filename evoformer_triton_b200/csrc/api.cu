@@ -10,15 +10,17 @@ namespace {
 
 thread_local int g_last_path = EVOATTN_PATH_NONE;
 thread_local int g_last_launches = 0;
-thread_local bool g_ctx_bound = false;
+thread_local int g_ctx_bound_device = -1;
 
 // Tensor maps are encoded through the driver API, which needs the device's primary context
 // to be current on the calling thread.  A thread that has made no runtime call yet (PyTorch's
-// autograd worker on its first backward) gets it bound here, once.
+// autograd worker on its first backward) gets it bound here, once per thread and device.
 void bind_context_once() {
-  if (!g_ctx_bound) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  if (g_ctx_bound_device != dev) {
     cudaFree(nullptr);  // the customary no-op that initialises / binds the primary context
-    g_ctx_bound = true;
+    g_ctx_bound_device = dev;
   }
 }
 
@@ -65,7 +67,6 @@ int validate_bwd(const evoattn_bwd_params* p) {
   int rc = validate_fwd(&p->fwd);
   if (rc) return rc;
   if (!p->d_o || !p->dq || !p->dk || !p->dv) return EVOATTN_ERR_NULL;
-  if (p->fwd.bias && !p->dbias) return EVOATTN_ERR_NULL;
   return EVOATTN_OK;
 }
 
@@ -98,6 +99,8 @@ bool use_sm100_bwd(const evoattn_bwd_params* p, const evo::Args& a) {
   if (!stride_ok16(p->do_stride, es) || !stride_ok16(p->dq_stride, es) || !stride_ok16(p->dk_stride, es) ||
       !stride_ok16(p->dv_stride, es))
     return false;
+  // d(pair_bias) leaves through a tensor map over its dense [B,H,R,R] layout: 16-byte base and rows
+  if (p->fwd.bias && p->dbias && ((((uintptr_t)p->dbias) & 15) != 0 || (p->fwd.R % 4) != 0)) return false;
   return evo::sm100_bwd_supported(p->fwd.dtype, a);
 }
 
@@ -110,17 +113,22 @@ constexpr int kMaxDevices = 64;
 void* g_static_scratch_addr[kMaxDevices] = {};
 std::mutex g_static_scratch_mutex;
 
-// Device address of the static scratch on the current device; looked up once per device.
+// Device address of the static scratch on the current device.  The lookup is repeated on every
+// call: it is cheap, it allocates nothing, and it is also what makes the device's primary
+// context current on a host thread that has made no CUDA call yet (a fresh worker thread, the
+// autograd engine's thread), which the tensor-map encoder needs.  The per-device table is only a
+// cross-check that the address never changes.
 int static_scratch_address(void** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return EVOATTN_ERR_CUDA;
-  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
-  if (!g_static_scratch_addr[dev]) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return EVOATTN_ERR_CUDA;
-    g_static_scratch_addr[dev] = ptr;
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return EVOATTN_ERR_CUDA;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_addr[dev]) g_static_scratch_addr[dev] = ptr;
+    else if (g_static_scratch_addr[dev] != ptr) return EVOATTN_ERR_CUDA;
   }
-  *out = g_static_scratch_addr[dev];
+  *out = ptr;
   return EVOATTN_OK;
 }
 
@@ -203,8 +211,8 @@ int evoattn_bwd_static_scratch(const evoattn_bwd_params* p, void* cuda_stream) {
   const bool fast = use_sm100_bwd(p, a);
   const size_t need = fast ? evo::sm100_bwd_workspace_bytes(p->fwd.dtype, a) : generic_bwd_workspace(a);
   if (need > EVOATTN_STATIC_SCRATCH_BYTES) return EVOATTN_ERR_WORKSPACE;
-  // Looking the symbol up also makes the device's primary context current on this thread,
-  // which the tensor-map encoder needs; nothing here allocates.
+  // Looking the symbol up (done on every call) also makes the device's primary context current
+  // on this thread, which the tensor-map encoder needs; nothing here allocates.
   void* scratch = nullptr;
   rc = static_scratch_address(&scratch);
   if (rc) return rc;

@@ -67,27 +67,6 @@ struct StepId16 {
   int b, h, s, it, g, j0;
 };
 
-template <class T> struct Pack16;
-template <> struct Pack16<__nv_bfloat16> {
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-template <> struct Pack16<__half> {
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-
-template <int N> __device__ __forceinline__ void setmaxnreg_inc16() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N> __device__ __forceinline__ void setmaxnreg_dec16() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-
 template <class T>
 __global__ void __launch_bounds__(kThreads16, 1)
 evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, const __grid_constant__ CUtensorMap tmQ,
@@ -201,7 +180,7 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
   (void)add_mask;
 
   if (warp >= kComputeWarps) {
-    setmaxnreg_dec16<24>();
+    setmaxnreg_dec<24>();
     if (warp == kComputeWarps) {
       const uint32_t leader = (lane == 0) ? 1u : 0u;  // the lane that issues; everything else is warp-uniform
       // =============================== control: TMA + MMA ===============================
@@ -238,21 +217,38 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
         const uint32_t base = (st_lo + buf * (L::kStage >> 4)) | kLoLbo;
         const uint32_t qa = base, da = base + (L::kTile >> 4), ka = base + 2 * (L::kTile >> 4);
         const uint32_t p_lo = p_lo0, ds_lo = ds_lo0;
-        // dV_j[s] += P^T dO_i : A = P read MN-major (M = j); K runs over the 128 query rows
+#ifndef EVO_OUT_INTERLEAVE
+#define EVO_OUT_INTERLEAVE 1
+#endif
+#if EVO_OUT_INTERLEAVE
+        // The three accumulators are independent chains: their MMAs are issued round-robin so that
+        // an MMA never follows one it depends on.
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk) {
+          // dV_j[s] += P^T dO_i : A = P read MN-major (M = j); K runs over the 128 query rows
+          mma_ss_if(leader, tmem + colDV + g * DP, pack_desc((p_lo + kk * 128) | kLoLboT, kHiPS), pack_desc(da + kk * RB, kHiOp),
+                    kIdescT, (kk > 0) ? 1u : first);
+          // dK_j[s] += dS^T Q_i
+          mma_ss_if(leader, tmem + colDK + g * DP, pack_desc((ds_lo + kk * 128) | kLoLboT, kHiPS), pack_desc(qa + kk * RB, kHiOp),
+                    kIdescT, (kk > 0) ? 1u : first);
+          // dQ_i[s] partial = dS K_j : A = dS K-major (K runs over the 128 keys)
+          mma_ss_if(leader, tmem + colDQ, pack_desc((ds_lo + (kk >> 2) * (BT * 128 >> 4) + (kk & 3) * 2) | kLoLbo, kHiPS),
+                    pack_desc(ka + kk * RB, kHiOp), kIdescQ, kk > 0 ? 1u : 0u);
+        }
+#else
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
           mma_ss_if(leader, tmem + colDV + g * DP, pack_desc((p_lo + kk * 128) | kLoLboT, kHiPS), pack_desc(da + kk * RB, kHiOp),
                     kIdescT, (kk > 0) ? 1u : first);
-        // dK_j[s] += dS^T Q_i
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
           mma_ss_if(leader, tmem + colDK + g * DP, pack_desc((ds_lo + kk * 128) | kLoLboT, kHiPS), pack_desc(qa + kk * RB, kHiOp),
                     kIdescT, (kk > 0) ? 1u : first);
-        // dQ_i[s] partial = dS K_j : A = dS K-major (K runs over the 128 keys)
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
           mma_ss_if(leader, tmem + colDQ, pack_desc((ds_lo + (kk >> 2) * (BT * 128 >> 4) + (kk & 3) * 2) | kLoLbo, kHiPS),
                     pack_desc(ka + kk * RB, kHiOp), kIdescQ, kk > 0 ? 1u : 0u);
+#endif
         mma_commit_if(leader, bar_out);
       };
 
@@ -353,7 +349,7 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
     }
   } else {
     // =============================== compute warps ===============================
-    setmaxnreg_inc16<112>();
+    setmaxnreg_inc<112>();
     const int qd = warp >> 2;    // column quarter: key columns qd*32 .. qd*32+31 of the tile
     const int half = qd >> 1;    // the half of S / dP (and of the P / dS tiles) those columns lie in
     const int row = (warp & 3) * 32 + lane;
@@ -390,14 +386,14 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
         T* kd = reinterpret_cast<T*>(a.dk) + off4(a.sdk, b, h, s, j) + qd * QD;
         T* vd = reinterpret_cast<T*>(a.dv) + off4(a.sdv, b, h, s, j) + qd * QD;
         uint4 pk, pv;
-        pk.x = Pack16<T>::pack(__uint_as_float(kr[0]) * scale, __uint_as_float(kr[1]) * scale);
-        pk.y = Pack16<T>::pack(__uint_as_float(kr[2]) * scale, __uint_as_float(kr[3]) * scale);
-        pk.z = Pack16<T>::pack(__uint_as_float(kr[4]) * scale, __uint_as_float(kr[5]) * scale);
-        pk.w = Pack16<T>::pack(__uint_as_float(kr[6]) * scale, __uint_as_float(kr[7]) * scale);
-        pv.x = Pack16<T>::pack(__uint_as_float(vr[0]), __uint_as_float(vr[1]));
-        pv.y = Pack16<T>::pack(__uint_as_float(vr[2]), __uint_as_float(vr[3]));
-        pv.z = Pack16<T>::pack(__uint_as_float(vr[4]), __uint_as_float(vr[5]));
-        pv.w = Pack16<T>::pack(__uint_as_float(vr[6]), __uint_as_float(vr[7]));
+        pk.x = Pack2<T>::pack(__uint_as_float(kr[0]) * scale, __uint_as_float(kr[1]) * scale);
+        pk.y = Pack2<T>::pack(__uint_as_float(kr[2]) * scale, __uint_as_float(kr[3]) * scale);
+        pk.z = Pack2<T>::pack(__uint_as_float(kr[4]) * scale, __uint_as_float(kr[5]) * scale);
+        pk.w = Pack2<T>::pack(__uint_as_float(kr[6]) * scale, __uint_as_float(kr[7]) * scale);
+        pv.x = Pack2<T>::pack(__uint_as_float(vr[0]), __uint_as_float(vr[1]));
+        pv.y = Pack2<T>::pack(__uint_as_float(vr[2]), __uint_as_float(vr[3]));
+        pv.z = Pack2<T>::pack(__uint_as_float(vr[4]), __uint_as_float(vr[5]));
+        pv.w = Pack2<T>::pack(__uint_as_float(vr[6]), __uint_as_float(vr[7]));
         *reinterpret_cast<uint4*>(kd) = pk;
         *reinterpret_cast<uint4*>(vd) = pv;
       }
@@ -557,10 +553,10 @@ evo_bwd16_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, co
 #pragma unroll
         for (int c8 = 0; c8 < 2; ++c8) {
           uint4 pk, dk;
-          pk.x = Pack16<T>::pack(p[c8 * 8 + 0], p[c8 * 8 + 1]); pk.y = Pack16<T>::pack(p[c8 * 8 + 2], p[c8 * 8 + 3]);
-          pk.z = Pack16<T>::pack(p[c8 * 8 + 4], p[c8 * 8 + 5]); pk.w = Pack16<T>::pack(p[c8 * 8 + 6], p[c8 * 8 + 7]);
-          dk.x = Pack16<T>::pack(ds[c8 * 8 + 0], ds[c8 * 8 + 1]); dk.y = Pack16<T>::pack(ds[c8 * 8 + 2], ds[c8 * 8 + 3]);
-          dk.z = Pack16<T>::pack(ds[c8 * 8 + 4], ds[c8 * 8 + 5]); dk.w = Pack16<T>::pack(ds[c8 * 8 + 6], ds[c8 * 8 + 7]);
+          pk.x = Pack2<T>::pack(p[c8 * 8 + 0], p[c8 * 8 + 1]); pk.y = Pack2<T>::pack(p[c8 * 8 + 2], p[c8 * 8 + 3]);
+          pk.z = Pack2<T>::pack(p[c8 * 8 + 4], p[c8 * 8 + 5]); pk.w = Pack2<T>::pack(p[c8 * 8 + 6], p[c8 * 8 + 7]);
+          dk.x = Pack2<T>::pack(ds[c8 * 8 + 0], ds[c8 * 8 + 1]); dk.y = Pack2<T>::pack(ds[c8 * 8 + 2], ds[c8 * 8 + 3]);
+          dk.z = Pack2<T>::pack(ds[c8 * 8 + 4], ds[c8 * 8 + 5]); dk.w = Pack2<T>::pack(ds[c8 * 8 + 6], ds[c8 * 8 + 7]);
           const int chunk16 = (((qd & 1) * 4 + sub * 2 + c8) ^ (row & 7)) << 4;
           *reinterpret_cast<uint4*>(prow + chunk16) = pk;
           *reinterpret_cast<uint4*>(drow + chunk16) = dk;

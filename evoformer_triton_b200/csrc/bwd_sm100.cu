@@ -69,27 +69,6 @@ struct BwdSmem {
   static constexpr size_t bytes = offBars + 128 + 1024;
 };
 
-template <class T> struct Pack2;
-template <> struct Pack2<__nv_bfloat16> {
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-template <> struct Pack2<__half> {
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-
-template <int N> __device__ __forceinline__ void setmaxnreg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
@@ -1031,36 +1010,11 @@ evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, c
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// d(pair_bias) either leaves the fused kernel through fp32 reductions (one 64 KB tile per CTA and
-// query tile) or is produced by the separate kernel of dbias_sm100.cu, which recomputes S and dP
-// but adds almost nothing to global memory.  On B200 the fused form measures faster for every
-// benchmark configuration (the recomputation costs more than the reductions), so the separate
-// kernel is opt-in: EVOATTN_SPLIT_DBIAS=1.
-// Head dimension 32 has two fused kernels: sixteen compute warps (bwd16_sm100.cu, the default:
-// it measures faster on B200) or eight (this file).  EVOATTN_BWD_WARPS=8 picks the latter.
-bool use_sixteen_warps() {
-  static const bool sixteen = [] {
-    const char* e = getenv("EVOATTN_BWD_WARPS");
-    return !(e && e[0] == '8');
-  }();
-  return sixteen;
-}
-
-bool split_dbias(const Args& a) {
-  static const bool want_split = [] {
-    const char* e = getenv("EVOATTN_SPLIT_DBIAS");
-    return e && e[0] == '1';
-  }();
-  return a.dbias != nullptr && want_split;
-}
-
 template <class T, int DP>
 int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* launches) {
   constexpr int G = GroupOf<DP>::G;
   using L = BwdSmem<DP, G>;
   Args a = a0;
-  const bool split = split_dbias(a0);
-  if (split) a.dbias = nullptr;  // the fused kernel skips its d_bias reductions
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;
   const size_t delta_bytes = align_up(rows * sizeof(float), 256);
   const size_t dq_bytes = rows * a.D * sizeof(float);
@@ -1075,11 +1029,10 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (!make_qkv_map(&tdo, a.d_o, a.sdo, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   CUtensorMap tdb;
   if (a.bias) {
-    // 128x16 chunks for the eight-warp kernel, 128x32 blocks for the others
-    const bool sixteen = (DP == 32 && use_sixteen_warps());
-    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, (DP <= 32 && !sixteen) ? 16 : 32)) return EVOATTN_ERR_CUDA;
+    // 128x16 chunks for the eight-warp kernel (D <= 16), 128x32 blocks for the others
+    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, (DP <= 16) ? 16 : 32)) return EVOATTN_ERR_CUDA;
     const Str3 dense{(long long)a.H * a.R * a.R, (long long)a.R * a.R, (long long)a.R};
-    if (!a.dbias) tdb = tq;  // d_bias comes from the separate kernel
+    if (!a.dbias) tdb = tq;  // the bias needs no gradient
     else if (!make_bias_map(&tdb, a.dbias, dense, a.B, a.H, a.R, BT, 32)) return EVOATTN_ERR_CUDA;
   } else {
     tb = tq;
@@ -1090,12 +1043,6 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
       cudaMemsetAsync(a.dbias, 0, (size_t)a.B * a.H * a.R * a.R * sizeof(float), st) != cudaSuccess)
     return EVOATTN_ERR_CUDA;
   delta_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(a);
-  if (split) {
-    Args ab = a;
-    ab.dbias = a0.dbias;
-    const int rc = launch_sm100_dbias(std::is_same<T, __nv_bfloat16>::value ? EVOATTN_BF16 : EVOATTN_FP16, ab, st, launches);
-    if (rc != EVOATTN_OK) return rc;
-  }
 
   const int NT = (a.R + BT - 1) / BT;
   const bool add = a.mask_kind == EVOATTN_MASK_ADD_F32 || a.mask_kind == EVOATTN_MASK_ADD_SAME;
@@ -1109,7 +1056,7 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       return EVOATTN_ERR_CUDA;
     const long long ctas = items < sms ? items : sms;
-    if (DP == 32 && use_sixteen_warps()) {
+    if (DP == 32) {
       const int rc = launch_sm100_bwd16(std::is_same<T, __nv_bfloat16>::value ? EVOATTN_BF16 : EVOATTN_FP16, a, dq_acc,
                                         items, (int)ctas, tq, tk, tv, tdo, tb, tdb, st);
       if (rc != EVOATTN_OK) return rc;

@@ -62,6 +62,21 @@ template <> __device__ __forceinline__ float from_float<float>(float x) { return
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
 
+// Two floats rounded to the 16-bit storage type, packed into one 32-bit word (first value low).
+template <class T> struct Pack2;
+template <> struct Pack2<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+template <> struct Pack2<__half> {
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
 __device__ __forceinline__ long long off4(const Str4& s, int b, int h, int ss, int r) {
   return (long long)b * s.b + (long long)h * s.h + (long long)ss * s.s + (long long)r * s.r;
 }

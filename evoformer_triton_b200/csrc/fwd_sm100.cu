@@ -66,27 +66,6 @@ struct Cfg {
   static constexpr int tmemWg = 2 * BN + 2 * DP;
 };
 
-template <class T> struct Pack2;
-template <> struct Pack2<__nv_bfloat16> {
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-template <> struct Pack2<__half> {
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-
-template <int N> __device__ __forceinline__ void setmaxnreg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-
 struct Item {
   int b, h, qt, sp;
 };
@@ -532,7 +511,16 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
-int g_num_sms = 0;
+// SM count of the current device (looked up once per device).
+int num_sms_of_current_device() {
+  static int table[64] = {};
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (table[dev] > 0) return table[dev];
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 0;
+  table[dev] = n;
+  return n;
+}
 
 template <class T, int DP>
 int launch_t(const Args& a, cudaStream_t st, int* launches) {
@@ -546,13 +534,8 @@ int launch_t(const Args& a, cudaStream_t st, int* launches) {
   } else {
     tb = tq;
   }
-  if (g_num_sms == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      return EVOATTN_ERR_CUDA;
-    g_num_sms = n;
-  }
+  const int g_num_sms = num_sms_of_current_device();
+  if (g_num_sms <= 0) return EVOATTN_ERR_CUDA;
   const int T_TILES = (a.R + BN - 1) / BN;
   const size_t smem = C::bytes(T_TILES * BN);
   const long long items = (long long)a.B * a.H * ((a.R + BM - 1) / BM) * ((a.S + 1) / 2);

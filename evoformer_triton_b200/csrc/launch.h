@@ -28,7 +28,4 @@ int launch_sm100_bwd16(int dtype, const Args& a, float* dq_acc, long long items,
                        const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tb,
                        const CUtensorMap& tdb, cudaStream_t st);
 
-// d(pair_bias) as a kernel of its own (dbias_sm100.cu): needs a.delta filled, writes a.dbias in full.
-int launch_sm100_dbias(int dtype, const Args& a, cudaStream_t st, int* launches);
-
 }  // namespace evo

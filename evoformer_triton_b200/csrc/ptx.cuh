@@ -337,6 +337,15 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// Move registers between the warps of a CTA (whole-warp instructions).  The requests of all
+// warps must sum to at most the launch-time pool, or `inc` blocks for ever.
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // Named barrier among `nthreads` threads (ids 1..15; id 0 is __syncthreads).
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

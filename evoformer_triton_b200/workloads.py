@@ -68,8 +68,6 @@ def make_keep_mask(w: Workload, gen: torch.Generator) -> Optional[torch.Tensor]:
         return None
     if kind == "bernoulli":
         keep = torch.rand((w.B, w.S, w.R), generator=gen) < float(arg)
-        # never leave a row without any key: the additive form of such a row is ill-conditioned
-        keep[..., 0] = True
     elif kind == "tail":
         n_drop = int(float(arg) * w.R)
         keep = (torch.arange(w.R) < w.R - n_drop).expand(w.B, w.S, w.R).clone()

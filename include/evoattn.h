@@ -91,9 +91,10 @@ typedef struct evoattn_bwd_params {
   void* dq;               /* out */
   void* dk;               /* out */
   void* dv;               /* out */
-  float* dbias;           /* out, fp32 [B,H,R,R] contiguous, or null when bias is null.
-                             Written in full (no need to zero it first):
-                             the sum over the S rows of dS (evoformer.py:458) */
+  float* dbias;           /* out, fp32 [B,H,R,R] contiguous: the sum over the S rows of dS
+                             (evoformer.py:458), written in full (no need to zero it first).
+                             Null when bias is null, or when the caller wants no gradient for
+                             the bias (the kernels then skip its reductions altogether) */
   int64_t do_stride[4];
   int64_t dq_stride[4];
   int64_t dk_stride[4];

@@ -47,7 +47,11 @@ def _worker(rank, world, port, q):
             errs = []
             for i, w in enumerate(want):
                 got = sharding.unshard_rows([p[i] for p in parts])
-                errs.append(bool(torch.equal(got, w)))           # same kernels on the same rows: bitwise
+                if i == 1:  # dQ is summed by fp32 reductions whose order is not fixed: equal to rounding
+                    den = float(w.float().abs().max())
+                    errs.append(float((got.float() - w.float()).abs().max()) / den < 4e-3)
+                else:       # O, dK, dV: same kernels on the same rows, fixed summation order: bitwise
+                    errs.append(bool(torch.equal(got, w)))
             db = [p[4].float() for p in parts]
             same_everywhere = all(torch.equal(db[0], d) for d in db[1:])
             rel = float((db[0] - fb.grad.cpu().float()).abs().max() / fb.grad.float().abs().max())
@@ -68,6 +72,10 @@ def test_two_gpu_sharded_matches_unsharded():
         p.start()
     for p in procs:
         p.join(300)
+    for p in procs:
+        if p.is_alive():  # a worker that outlived the limit: end it (exact process, not a pattern)
+            p.terminate()
+            p.join(10)
         assert p.exitcode == 0, f"worker exited with {p.exitcode}"
     errs, same_everywhere, rel = q.get(timeout=10)
     assert all(errs), f"O/dQ/dK/dV of the shards differ from the unsharded run: {errs}"

@@ -85,6 +85,49 @@ def test_static_scratch_backward_matches_ordinary_backward(cfg):
             assert _rel(a, b) < 4e-3, (attempt, name, _rel(a, b))
 
 
+def test_static_scratch_from_a_fresh_host_thread_and_near_the_limit():
+    """Two things the small cases above do not reach: a call made from a host thread that has never
+    touched CUDA (such a thread has no current context until the entry point binds one; PyTorch's
+    autograd engine calls backward from a thread like that), and a request that fills most of the
+    array (the headline workload: B=1, H=8, S=128, R=384, D=32 needs 51.9 MB of the 64 MiB)."""
+    import threading
+    from evoformer_triton_b200 import _lib, attention
+    lib = _lib.load()
+    B, H, S, R, D, dtype = 1, 8, 128, 384, 32, torch.bfloat16
+    q, k, v, d_o, mask, bias = _make(B, H, S, R, D, dtype, seed=77)
+    o, lse = attention.attention_forward(q, k, v, mask, bias, D ** -0.5)
+    stream_handle = torch.cuda.current_stream().cuda_stream
+
+    ref = _fresh_outs(q, bias)
+    p = _bwd_params(q, k, v, o, lse, mask, bias, d_o, ref)
+    need = lib.evoattn_bwd_workspace_bytes(C.byref(p))
+    assert (48 << 20) < need <= _lib.STATIC_SCRATCH_BYTES
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), need
+    assert lib.evoattn_bwd(C.byref(p), C.c_void_p(stream_handle)) == 0
+    torch.cuda.synchronize()
+
+    got = _fresh_outs(q, bias)
+    p2 = _bwd_params(q, k, v, o, lse, mask, bias, d_o, got)
+    p2.workspace, p2.workspace_bytes = None, 0
+    rcs = []
+
+    def call():  # no torch call in here: nothing else binds a context for this thread
+        rcs.append(lib.evoattn_bwd_static_scratch(C.byref(p2), C.c_void_p(stream_handle)))
+
+    for _ in range(2):  # the second thread finds the address table already filled
+        t = threading.Thread(target=call)
+        t.start()
+        t.join(120)
+        assert not t.is_alive()
+        torch.cuda.synchronize()
+    assert rcs == [0, 0], rcs
+    attention.check_device_status()
+    for name, a, b in zip(("dq", "dk", "dv", "dbias"), got, ref):
+        assert torch.isfinite(a).all(), name
+        assert _rel(a, b) < 4e-3, (name, _rel(a, b))
+
+
 def test_static_scratch_rejects_requests_beyond_its_array():
     from evoformer_triton_b200 import _lib, attention
     lib = _lib.load()
