@@ -1082,7 +1082,13 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
 template <class T>
 int launch_d(const Args& a, void* ws, size_t ws_bytes, cudaStream_t st, int* launches) {
   if (a.D <= 16) return launch_t<T, 16>(a, ws, ws_bytes, st, launches);
+#ifndef EVO_USE_BWD16
+  if (a.D <= 32)
+    return launch_sm100_bwdt(std::is_same<T, __nv_bfloat16>::value ? EVOATTN_BF16 : EVOATTN_FP16, a, ws, ws_bytes, st,
+                             launches);
+#else
   if (a.D <= 32) return launch_t<T, 32>(a, ws, ws_bytes, st, launches);
+#endif
   return launch_t<T, 64>(a, ws, ws_bytes, st, launches);
 }
 
@@ -1096,6 +1102,9 @@ bool sm100_bwd_supported(int dtype, const Args& a) {
 }
 
 size_t sm100_bwd_workspace_bytes(int, const Args& a) {
+#ifndef EVO_USE_BWD16
+  if (a.D > 16 && a.D <= 32) return sm100_bwdt_workspace_bytes(a);
+#endif
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;
   return align_up(rows * sizeof(float), 256) + rows * a.D * sizeof(float);
 }

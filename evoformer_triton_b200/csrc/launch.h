@@ -28,4 +28,9 @@ int launch_sm100_bwd16(int dtype, const Args& a, float* dq_acc, long long items,
                        const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tb,
                        const CUtensorMap& tdb, cudaStream_t st);
 
+// The fused backward with transposed score tiles (bwdt_sm100.cu; head dimensions 17..32).
+size_t sm100_bwdt_workspace_bytes(const Args& a);
+int launch_sm100_bwdt(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
+                      int* launches);
+
 }  // namespace evo

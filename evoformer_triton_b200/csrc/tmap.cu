@@ -79,4 +79,32 @@ bool make_rows_f32_map(CUtensorMap* out, const float* base, int D, int R, long l
   return r == CUDA_SUCCESS;
 }
 
+bool make_bias_plain_map(CUtensorMap* out, const float* base, const Str3& st, int B, int H, int R, int box_i,
+                         int box_j) {
+  std::call_once(g_once, resolve);
+  if (!g_encode) return false;
+  const uint64_t row = static_cast<uint64_t>(R) * 4;
+  cuuint64_t dims[4] = {(cuuint64_t)R, (cuuint64_t)R, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {fix_stride(st.c, 4, row, R), fix_stride(st.b, 4, row, H), fix_stride(st.a, 4, row, B)};
+  cuuint32_t box[4] = {(cuuint32_t)box_j, (cuuint32_t)box_i, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool make_stats_map(CUtensorMap* out, const float* base, int BH, int S, int R, int box_r) {
+  std::call_once(g_once, resolve);
+  if (!g_encode) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)R, (cuuint64_t)S, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)R * 4, (cuuint64_t)R * 4 * (cuuint64_t)S};
+  cuuint32_t box[3] = {(cuuint32_t)box_r, 1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 }  // namespace evo

@@ -23,4 +23,13 @@ bool make_bias_map(CUtensorMap* out, const float* base, const Str3& stride_elems
 // (D, R, slabs) with box (box_d, box_r, 1); rows and columns beyond R and D are clipped.
 bool make_rows_f32_map(CUtensorMap* out, const float* base, int D, int R, long long slabs, int box_d, int box_r);
 
+// fp32 [B,H,R,R] pair bias (or its dense gradient) as a 4-D map (R_j, R_i, H, B) with an
+// unswizzled box (box_j, box_i, 1, 1): rows of box_j floats land back to back in shared memory.
+bool make_bias_plain_map(CUtensorMap* out, const float* base, const Str3& stride_elems, int B, int H, int R, int box_i,
+                         int box_j);
+
+// Contiguous fp32 per-row statistics [B*H, S, R] as a 3-D map (R, S, B*H) with box (box_r, 1, 1);
+// rows beyond R and MSA rows beyond S read as zero.
+bool make_stats_map(CUtensorMap* out, const float* base, int BH, int S, int R, int box_r);
+
 }  // namespace evo
