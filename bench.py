@@ -30,9 +30,21 @@ from evoformer_triton_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
 
 METRIC = "evoformer_attn_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
-# profiles/fwd_kernel_C2.md and profiles/bwd_kernel_C2.md (workload C2 only).
-NCU_DRAM_BYTES = {"C2": {"forward kernel": 80339200 + 8521216, "backward call": 163806208 + 58541824}}
+
+
+def ncu_dram_bytes(workload: str, kernel: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the named kernel, as recorded
+    from an Nsight Compute capture of this benchmark (profiles/ncu_dram_bytes.json: workload ->
+    kernel -> bytes and the capture it came from); None where no capture has been recorded."""
+    path = os.path.join(ROOT, "profiles", "ncu_dram_bytes.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f).get(workload, {}).get(kernel)
+    except (OSError, ValueError):
+        return None, None
+    if not rec:
+        return None, None
+    return int(rec["bytes"]), rec.get("source")
 
 
 def measured_peaks():
@@ -163,8 +175,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="C2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--ref-rows", type=int, default=32, help="MSA rows per step of the CPU reference arm")
-    ap.add_argument("--cpu-baseline-rows", type=int, default=64)
+    ap.add_argument("--ref-rows", type=int, default=128, help="MSA rows per step of the CPU reference arm (capped at the workload's)")
+    ap.add_argument("--cpu-baseline-rows", type=int, default=128)
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every rank holds the workload's N_seq rows of its own; strong: the workload's rows are split over the ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -190,7 +204,14 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     w = WORKLOADS[args.workload]
-    # weak scaling: every rank holds w.S MSA rows of its own; the job has w.S * world rows
+    if args.scaling == "strong":
+        # strong scaling: one job of w.S MSA rows, split over the ranks (kernel-view rows)
+        if w.S % world:
+            raise SystemExit(f"--scaling strong needs N_seq={w.S} divisible by the number of GPUs")
+        w_job, w = w, w.with_rows(w.S // world)
+    else:
+        # weak scaling: every rank holds w.S MSA rows of its own; the job has w.S * world rows
+        w_job = w.with_rows(w.S * world)
     x = make_inputs(w, rows=w.S, row_offset=rank, device=dev)
     Q, K, V, dO = x["Q"], x["K"], x["V"], x["dO"]
     mask, bias = x["res_mask"], x["pair_bias"]
@@ -239,8 +260,23 @@ def main():
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     ms_per_step = float(total_ms.item()) / args.steps
+    med = torch.tensor([statistics.median(step_ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(med, op=dist.ReduceOp.MAX)
+    ms_per_step_median = float(med.item())
     flops_job = w.flops_fwd_bwd * world
     value = flops_job / (ms_per_step * 1e-3) / 1e12
+
+    # ---- peak device memory of one forward + backward of the op, over what was allocated before it
+    # (inputs, gradients of earlier steps dropped, the flush buffer): what memory_benchmark.py:38 reports
+    zero_grads()
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats(dev)
+    mem_before = torch.cuda.memory_allocated(dev)
+    step()
+    torch.cuda.synchronize()
+    op_peak_mem = torch.cuda.max_memory_allocated(dev) - mem_before
+    zero_grads()
 
     # ---- per-kernel split (forward kernel, backward call), same flush discipline
     with torch.no_grad():
@@ -267,13 +303,15 @@ def main():
     dom_flops = (w.flops_fwd_bwd - w.flops_fwd) if dom_bwd else w.flops_fwd
     dom_ms = bwd_ms if dom_bwd else fwd_ms
     achieved = dom_flops / (dom_ms * 1e-3) / 1e12
+    traffic, traffic_src = ncu_dram_bytes(w.name if args.scaling == "weak" else "", "backward kernel" if dom_bwd else "forward kernel")
     roofline = {
         "bound": "tensor", "kernel": "backward call" if dom_bwd else "forward kernel",
         "launches_in_call": bwd_launches if dom_bwd else attention.launches["fwd"],
         "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
         "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
-        "traffic": NCU_DRAM_BYTES.get(w.name, {}).get("backward call" if dom_bwd else "forward kernel"),
-        "traffic_unit": "bytes per launch (ncu DRAM read+write of the dominant kernel)",
+        "traffic": traffic,
+        "traffic_unit": "bytes per launch of the call's main kernel (ncu dram__bytes_read.sum + dram__bytes_write.sum)",
+        "traffic_source": traffic_src,
         "algorithmic_bytes": algorithmic_bytes(w, backward=dom_bwd),
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "fwd_tflops": w.flops_fwd / (fwd_ms * 1e-3) / 1e12,
@@ -332,7 +370,7 @@ def main():
 
         run(2)
         latency_ms = run(1)
-        k_e2e = max(8, args.steps // 2)
+        k_e2e = max(8, args.steps)
         e2e_ms = run(k_e2e)
         d2h = sum(t.numel() * t.element_size() for t in host_out)
         t_e2e = torch.tensor([e2e_ms, latency_ms], dtype=torch.float64, device=dev)
@@ -343,7 +381,6 @@ def main():
                "steps": k_e2e, "single_step_latency_ms": float(t_e2e[1].item()),
                "how": "copies of neighbouring steps overlap the compute (3 streams, 2 input sets)"}
     evo.check_device_status()
-    peak_mem = torch.cuda.max_memory_allocated(dev)
 
     if rank == 0:
         cpu = None
@@ -358,15 +395,17 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": dtype_name(w.dtype), "data": "synthetic",
-            "config": {"workload": describe(w), "rows_per_gpu": w.S, "global_rows": w.S * world,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": dtype_name(w.dtype), "data": "synthetic",
+            "ms_per_step_median": ms_per_step_median,
+            "config": {"workload": describe(w_job if args.scaling == "strong" else w), "rows_per_gpu": w.S,
+                       "global_rows": w.S * world,
                        "l2": "256 MB buffer written between timed steps",
                        "collective": "NCCL all-reduce of d(pair_bias) inside the step" if world > 1 else "none",
                        "paths": {k: {0: "none", 1: "cuda-core", 2: "tcgen05"}[v] for k, v in paths.items()}},
             "frac_of_bf16_peak": value / (peaks["tflops"] * world),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps,
-            "peak_mem_bytes": peak_mem, "clocks": clocks,
+            "op_peak_mem_bytes": op_peak_mem, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -41,7 +41,7 @@ constexpr int G = 3;      // MSA rows per work item
 constexpr int kCW = 16;   // compute warps
 constexpr int kThreadsT = 640;  // 16 compute + 4 service warps, five warps per scheduler
 constexpr int kComputeRegs = 112, kServiceRegs = 24;  // after setmaxnreg; the launch-time pool must hold their sum
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int DP>
@@ -52,15 +52,16 @@ struct SmemT {
   static constexpr int kStage = 2 * kTile + 2 * kVec;        // Q, dO, -lse*log2e, delta of one step
   static constexpr int kDS = BT * BT * 2;                    // dS^T: two halves of [128 keys][64 queries]
   static constexpr int kBias = BT * BT * 4;                  // pair-bias tile [128 i][128 j] fp32, unswizzled
-  static constexpr int kDQ = BT * DP * 4;                    // staging tile of a dQ partial
+  static constexpr int kOutWarp = 2048;                      // per compute warp: staging of a d_bias chunk or a dQ block
   static constexpr int offKV = 0;                            // [g][K, V], resident for the whole item
   static constexpr int offStage = offKV + 2 * G * kTile;
   static constexpr int offDS = offStage + kStages * kStage;
   static constexpr int offBias = offDS + kDS;
-  static constexpr int offDQ = offBias + kBias;
-  static constexpr int offBars = offDQ + kDQ;
-  static constexpr size_t bytes = offBars + 512 + 1024;
+  static constexpr int offOut = offBias + kBias;
+  static constexpr int offBars = offOut + kCW * kOutWarp;
+  static constexpr size_t bytes = offBars + 512 + 1024;  // 25 barriers and three words
   static_assert(offDS % 1024 == 0 && kStage % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+  static_assert(bytes <= 232448, "shared memory budget of one CTA");
 };
 
 struct StepT {
@@ -88,26 +89,21 @@ constexpr int kTrace0 = 20;
 #else
 #define TR(role, id)
 #endif
-#ifdef EVO_PROF
-__device__ long long g_prof[8][16];
-#define PROF_DECL long long prof_[16] = {0}; long long prof_t0_ = 0;
-#define PROF_BEGIN prof_t0_ = clock64();
-#define PROF_END(id) prof_[id] += clock64() - prof_t0_;
-#define PROF_FLUSH(row) if (blockIdx.x == 0 && lane == 0) { for (int i_ = 0; i_ < 16; ++i_) g_prof[row][i_] = prof_[i_]; }
-#else
-#define PROF_DECL
-#define PROF_BEGIN
-#define PROF_END(id)
-#define PROF_FLUSH(row)
-#endif
 
 // delta[b,h,s,i] = <dO_i, O_i> (evoformer.py:299-326) and nl = -lse*log2e, one thread per row.
 // A row whose keys were all dropped carries lse = -FLT_MAX from the forward; its nl is +inf, which
-// the fused kernel recognises.
+// the fused kernel recognises.  The block also clears its 256 rows of the fp32 dQ accumulator
+// (contiguous in memory), which saves a separate pass over that buffer.
 template <class T>
-__global__ void __launch_bounds__(256) prep_kernel(Args a, float* __restrict__ nl) {
-  const long long row = (long long)blockIdx.x * 256 + threadIdx.x;
+__global__ void __launch_bounds__(256) prep_kernel(Args a, float* __restrict__ nl, float* __restrict__ dq_acc) {
   const long long rows = (long long)a.B * a.H * a.S * a.R;
+  {
+    const long long f4_first = (long long)blockIdx.x * 256 * (a.D / 4);
+    const long long f4_end = min(rows, (long long)(blockIdx.x + 1) * 256) * (a.D / 4);
+    float4* dst = reinterpret_cast<float4*>(dq_acc);
+    for (long long e = f4_first + threadIdx.x; e < f4_end; e += 256) dst[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const long long row = (long long)blockIdx.x * 256 + threadIdx.x;
   if (row >= rows) return;
   const int i = (int)(row % a.R);
   long long sl = row / a.R;
@@ -164,7 +160,6 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
   constexpr int RB = L::RB;
   constexpr uint32_t SWZ = swizzle_code_for_row_bytes(RB);
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-  constexpr int QD = DP / 4;  // dQ / dK / dV columns drained by one compute warp
   static_assert(DP == 32, "instantiated for a padded head dimension of 32");
   constexpr int kTmemCols = 512;
   // TMEM: two (S^T, dP^T) half-tile buffers, the per-row dV and dK accumulators, two dQ partials
@@ -178,25 +173,23 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
   uint8_t* sStage = smem + L::offStage;
   uint8_t* sDS = smem + L::offDS;
   uint8_t* sBias = smem + L::offBias;
-  uint8_t* sDQ = smem + L::offDQ;
+  uint8_t* sOut = smem + L::offOut;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBars);
   const uint32_t bars_s = smem_u32(bars);
   const Bar kv_full{bars_s + 8 * 0};     // [G] K and V of row g of the current item landed
   const Bar kv_empty{bars_s + 8 * 3};    // [G] ... and every MMA that reads them has completed
-  const Bar st_full{bars_s + 8 * 6};     // [3] Q, dO and the statistics vectors of a step landed
-  const Bar st_empty{bars_s + 8 * 9};    // [3] ... the step's last dV/dK MMA has completed
-  const Bar sd_full{bars_s + 8 * 12};    // [2] S^T and dP^T of a mini-step are in TMEM buffer h
-  const Bar cdone{bars_s + 8 * 14};      // [2] the compute warps finished a mini-step (P^T, dS^T, dS stored)
-  const Bar b_full{bars_s + 8 * 16};     // [2] half h (64 queries) of the pair-bias tile landed
-  const Bar b_done{bars_s + 8 * 18};     // [2] ... has been read for the last time (and holds d_bias after a flush)
-  const Bar ds_empty{bars_s + 8 * 20};   // the dQ MMAs of a step have read the dS tile
-  const Bar dq_full{bars_s + 8 * 21};    // [2] the dQ partial of a step is complete in TMEM
-  const Bar dqs_full{bars_s + 8 * 23};   // the compute warps staged a dQ partial in shared memory
-  const Bar dqs_empty{bars_s + 8 * 24};  // its reduction has read the staging tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 26);
+  const Bar st_full{bars_s + 8 * 6};     // [2] Q, dO and the statistics vectors of a step landed
+  const Bar st_empty{bars_s + 8 * 8};    // [2] ... the step's last dV/dK MMAs have completed
+  const Bar sd_full{bars_s + 8 * 10};    // [2] S^T and dP^T of half h of a step are in TMEM buffer h
+  const Bar cdone{bars_s + 8 * 12};      // [2] the warps of half h have P^T and dS^T of a step in TMEM (for the dV/dK MMAs)
+  const Bar sdone{bars_s + 8 * 23};      // [2] ... and have stored their half of dS in shared memory (for the dQ MMAs)
+  const Bar b_full{bars_s + 8 * 14};     // [2] half h (64 queries) of the pair-bias tile landed
+  const Bar b_done{bars_s + 8 * 16};     // [2] ... has been read for the last time
+  const Bar ds_empty{bars_s + 8 * 18};   // the dQ MMAs of a step have read the dS tile
+  const Bar dq_full{bars_s + 8 * 19};    // [2] the dQ partial of a step is complete in TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 22);  // (bars 23, 24: sdone)
   const uint32_t abort_s = smem_u32(const_cast<int*>(abort_flag));
-  volatile uint32_t* scratch = reinterpret_cast<volatile uint32_t*>(bars + 27);  // written, never read
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NT = (a.R + BT - 1) / BT;
@@ -238,15 +231,14 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
 
   if (tid == 0) {
     for (int i = 0; i < G; ++i) { mbar_init(bars + 0 + i, 1); mbar_init(bars + 3 + i, 3); }  // kv_full; kv_empty: three MMA warps read K/V
-    for (int i = 0; i < kStages; ++i) { mbar_init(bars + 6 + i, 1); mbar_init(bars + 9 + i, 2); }  // st_full, st_empty
+    for (int i = 0; i < kStages; ++i) { mbar_init(bars + 6 + i, 1); mbar_init(bars + 8 + i, 2); }  // st_full, st_empty
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bars + 12 + i, 2); mbar_init(bars + 14 + i, kCW);   // sd_full, cdone
-      mbar_init(bars + 16 + i, 1); mbar_init(bars + 18 + i, kCW);   // b_full, b_done
-      mbar_init(bars + 21 + i, 1);                                  // dq_full
+      mbar_init(bars + 10 + i, 2); mbar_init(bars + 12 + i, kCW / 2);  // sd_full, cdone
+      mbar_init(bars + 14 + i, 1); mbar_init(bars + 16 + i, kCW / 2);  // b_full, b_done
+      mbar_init(bars + 19 + i, 1);                                     // dq_full
+      mbar_init(bars + 23 + i, kCW / 2);                               // sdone
     }
-    mbar_init(bars + 20, 1);    // ds_empty
-    mbar_init(bars + 23, kCW);  // dqs_full
-    mbar_init(bars + 24, 1);    // dqs_empty
+    mbar_init(bars + 18, 1);  // ds_empty
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
     prefetch_tmap(&tmNL); prefetch_tmap(&tmDL); prefetch_tmap(&tmDQ);
@@ -266,16 +258,17 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
     setmaxnreg_dec<kServiceRegs>();
     if (warp <= kCW + 1) {
       // =============================== tensor-core issuers: warp 16 (S^T, dV), warp 17 (dP^T, dK) ==========
-      // Issuing a tcgen05.mma costs the issuing warp about fifty cycles, so the 32 MMAs of a step are
-      // spread over three warps on three schedulers.  A thread's MMAs run in issue order, MMAs of
+      // Issuing a tcgen05.mma costs the issuing warp fifty cycles and more, so the 32 MMAs of a step
+      // are spread over three warps on three schedulers.  A thread's MMAs run in issue order, MMAs of
       // different threads in no particular order, so the split follows the data: warp 16 owns the
       // S^T columns of both buffers (S^T = K_j Q_i^T in, dV_j += P^T dO_i out), warp 17 the dP^T columns
       // (dP^T = V_j dO_i^T in, dK_j += dS^T Q_i out): the MMA that overwrites a buffer is always issued
       // by the thread that issued the MMAs reading it.  Warp 18 issues dQ_i = dS K_j, which depends on
-      // neither.  All lanes stay converged (descriptors live in uniform registers); `leader`
-      // predicates the instructions that one thread must issue.
+      // neither.  One lane of each warp runs the whole issue loop (measured: a tcgen05.mma issued from a
+      // single-thread branch costs the warp a quarter less than the same instruction predicated on a
+      // leader lane in a converged warp).
       const bool isA = (warp == kCW);
-      const uint32_t leader = (lane == 0) ? 1u : 0u;
+      if (lane == 0) {
       constexpr uint32_t kIdescSD = make_idesc(kBf16, false, false, BT, HT);   // S^T, dP^T: K-major operands, N = 64
       constexpr uint32_t kIdescOut = make_idesc(kBf16, false, true, BT, DP);   // dV, dK: A from TMEM, B MN-major
       constexpr uint32_t kHiOp = static_cast<uint32_t>(make_sdesc_const(16, 8 * RB, SWZ) >> 32);
@@ -288,7 +281,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       const uint32_t col_in0 = isA ? colS0 : colDP0, col_in1 = isA ? colS1 : colDP1;
       const uint32_t col_acc = isA ? colDV : colDK;
 
-      auto issue_in = [&](int n, int h) {  // S^T (warp 16) or dP^T (warp 17) of mini-step (n, h)
+      auto issue_in = [&](int n, int h) {  // S^T (warp 16) or dP^T (warp 17) of half h of step n
         const int nn = n % SPI, g = nn % G, it = nn / G, stg = n % kStages;
         if (h == 0) {
           mbar_wait(st_full + stg, (n / kStages) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
@@ -298,58 +291,40 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
         const uint32_t ka = (kv_lo + (2 * g) * (L::kTile >> 4)) | kLoLbo;
         const uint32_t qa = (in_lo + stg * (L::kStage >> 4) + h * ((HT * RB) >> 4)) | kLoLbo;
         const uint32_t tD = tmem + (h ? col_in1 : col_in0);
-#pragma unroll
-        for (int kk = 0; kk < DP / 16; ++kk)
-          mma_ss_if(leader, tD, pack_desc(ka + kk * 2, kHiOp), pack_desc(qa + kk * 2, kHiOp), kIdescSD, kk > 0 ? 1u : 0u);
-        mma_commit_if(leader, sd_full + h);
-        // the item's last read of this warp's K or V tile of row g
-        if (h == 1 && it == NT - 1) mma_commit_if(leader, kv_empty + g);
+        static_assert(DP == 32, "two K slices");
+        // (the second commit: the item's last read of this warp's K or V tile of row g)
+        mma_ss_x2_commit(tD, ka, qa, kHiOp, 2, kIdescSD, (sd_full + h).a, (h == 1 && it == NT - 1) ? (kv_empty + g).a : 0u);
       };
       auto issue_out = [&](int n, int h) {  // dV_j[g] += P^T dO_i (warp 16) or dK_j[g] += dS^T Q_i (warp 17)
         const int nn = n % SPI, g = nn % G, it = nn / G, stg = n % kStages;
-        const uint32_t first = (it == 0 && h == 0) ? 0u : 1u;  // the item's first mini-step of row g overwrites
+        const uint32_t first = (it == 0 && h == 0) ? 0u : 1u;  // the item's first half-step of row g overwrites
         const uint32_t ba = (out_lo + stg * (L::kStage >> 4) + (4 * h) * kRowBlk) | kLoLbo;
         const uint32_t tA = tmem + (h ? col_in1 : col_in0);
-#pragma unroll
-        for (int kk = 0; kk < HT / 16; ++kk)  // A = 16 queries of P^T / dS^T (8 packed TMEM columns), B = their dO / Q rows
-          mma_ts_if(leader, tmem + col_acc + g * DP, tA + 16 * kk, pack_desc(ba + kk * kRowBlk, kHiOp), kIdescOut,
-                    kk > 0 ? 1u : first);
-        if (h == 1) mma_commit_if(leader, st_empty + stg);
+        // A = 16 queries of P^T / dS^T (8 packed TMEM columns), B = their dO / Q rows
+        mma_ts_x4(tmem + col_acc + g * DP, tA, ba, kHiOp, kRowBlk, kIdescOut, first);
+        if (h == 1) mma_commit_if(1u, st_empty + stg);
       };
 
-      PROF_DECL
       if (total_steps > 0) {
         issue_in(0, 0);
         issue_in(0, 1);
       }
-#ifdef EVO_PROF
-      const long long tl0 = clock64();
-#endif
       for (int n = 0; n < total_steps; ++n) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          PROF_BEGIN
           mbar_wait(cdone + h, n & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
-          PROF_END(h)
           if (isA) { TR(1, 3 * h) }
           tc_fence_after();
-          PROF_BEGIN
           issue_out(n, h);
-          PROF_END(2)
           if (isA) { TR(1, 3 * h + 1) }
-          PROF_BEGIN
           if (n + 1 < total_steps) issue_in(n + 1, h);
-          PROF_END(4 + h)
           if (isA) { TR(1, 3 * h + 2) }
         }
       }
-#ifdef EVO_PROF
-      prof_[15] = clock64() - tl0; prof_[14] = total_steps;
-      if (isA) { PROF_FLUSH(1) }
-#endif
+      }  // lane 0
     } else if (warp == kCW + 2) {
-      // =============================== tensor-core issuer of dQ ===============================
-      const uint32_t leader = (lane == 0) ? 1u : 0u;
+      // =============================== tensor-core issuer of dQ; pair-bias loads ===============================
+      if (lane == 0) {
       constexpr uint32_t kIdescDQ = make_idesc(kBf16, true, true, BT, DP);     // A = dS^T read MN-major, B = K MN-major
       constexpr uint32_t kHiOp = static_cast<uint32_t>(make_sdesc_const(16, 8 * RB, SWZ) >> 32);
       constexpr uint32_t kHiDS = static_cast<uint32_t>(make_sdesc_const(16, 1024, SWZ_128B) >> 32);
@@ -357,98 +332,52 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       constexpr uint32_t kLoLboDS = static_cast<uint32_t>(make_sdesc_const(BT * 128, 0, 0) & 0xffffffffu);
       constexpr uint32_t kRowBlk = (16 * RB) >> 4;
       const uint32_t kv_lo = smem_u32(sKV) >> 4, ds_lo = smem_u32(sDS) >> 4;
-      PROF_DECL
-      StepT dprev = decode(0);  // position of the step whose dQ partial is sent next
-      auto send_dq = [&](int m) {
-        mbar_wait(dqs_full, m & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
-        if (lane == 0) {
-          if (dprev.s < a.S) {
-            tma_reduce_add_3d_s(&tmDQ, smem_u32(sDQ), 0, dprev.it * BT, (dprev.b * a.H + dprev.h) * a.S + dprev.s);
-            tma_commit_group();
-            tma_wait_group_read0();
-          }
-          mbar_arrive(dqs_empty);
-        }
-        __syncwarp();
-        dprev = advance(dprev, m + 1);
-      };
-      // Pair bias in, d(pair_bias) out.  The bias tile (i, j) is the same for the G rows of a group.
-      // After the group's last step the compute warps hand each half (64 queries) back holding the
-      // d_bias values instead (same place, same layout); this warp adds it to d_bias in global memory
-      // with one bulk tensor reduction and then loads the next tile's half over it.
+      const uint32_t sBias_s = smem_u32(sBias);
+      // The bias tile (i, j) is the same for the G rows of a group; each half (64 queries) is loaded
+      // for the group's first step and replaced as soon as the warps of that half have read it for
+      // the last time.
       auto load_bias = [&](int t, int h) {
         const StepT d = decode(t * G);
         if (lane == 0) {
           mbar_expect_tx(b_full + h, L::kBias / 2);
-          tma_load_4d_s(smem_u32(sBias) + h * (L::kBias / 2), &tmB, (b_full + h).a, d.j0, d.it * BT + h * HT, d.h, d.b);
+          tma_load_4d_s(sBias_s + h * (L::kBias / 2), &tmB, (b_full + h).a, d.j0, d.it * BT + h * HT, d.h, d.b);
         }
-        __syncwarp();
       };
       const int tiles = my_items * NT;
       if (has_bias && tiles > 0) { load_bias(0, 0); load_bias(0, 1); }
-      // d_bias half h of tile t out (if wanted), bias half h of tile t+1 in
-      auto turn_bias = [&](int t, int h) {
-        const StepT d = decode(t * G);
-        mbar_wait(b_done + h, t & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
-        if (flush_dbias && lane == 0) {
-          tma_reduce_add_4d_s(&tmDB, smem_u32(sBias) + h * (L::kBias / 2), d.j0, d.it * BT + h * HT, d.h, d.b);
-          tma_commit_group();
-          tma_wait_group_read0();
-        }
-        __syncwarp();
-        if (t + 1 < tiles) load_bias(t + 1, h);
-      };
       for (int n = 0; n < total_steps; ++n) {
-        const int nn = n % SPI, g = nn % G, it = nn / G;
-        const bool turn = has_bias && g == G - 1;  // the group's last step: the halves come back one by one
-        if (turn) {
-          mbar_wait(cdone + 0, n & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
-          turn_bias(n / G, 0);
+        const int nn = n % SPI, g = nn % G, it = nn / G, t = n / G;
+        const bool turn = has_bias && g == G - 1 && t + 1 < tiles;  // the group's last step: the halves come back
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mbar_wait(sdone + h, n & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
+          if (turn) {
+            mbar_wait(b_done + h, t & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
+            load_bias(t + 1, h);
+          }
         }
-        PROF_BEGIN
-        mbar_wait(cdone + 1, n & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
-        PROF_END(0)
         TR(2, 0)
-        if (turn) turn_bias(n / G, 1);
-        TR(2, 1)
         tc_fence_after();
-        PROF_BEGIN
         const uint32_t ka = (kv_lo + (2 * g) * (L::kTile >> 4)) | kLoLbo;
         // dQ_i partial = dS K_j : A = dS^T tile [key][query] read MN-major (M = query), K runs over the keys
-#pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)
-          mma_ss_if(leader, tmem + colDQ + (n & 1) * DP, pack_desc((ds_lo + kk * 128) | kLoLboDS, kHiDS),
-                    pack_desc(ka + kk * kRowBlk, kHiOp), kIdescDQ, kk > 0 ? 1u : 0u);
-        mma_commit_if(leader, dq_full + (n & 1));
-        mma_commit_if(leader, ds_empty);
-        if (it == NT - 1) mma_commit_if(leader, kv_empty + g);
-        PROF_END(1)
+        mma_ss_x8(tmem + colDQ + (n & 1) * DP, ds_lo | kLoLboDS, kHiDS, 128, ka, kHiOp, kRowBlk, kIdescDQ);
+        mma_commit_if(1u, dq_full + (n & 1));
+        mma_commit_if(1u, ds_empty);
+        if (it == NT - 1) mma_commit_if(1u, kv_empty + g);
         TR(2, 2)
-        // The dQ partial of step n-1 was staged by the compute warps right after they finished step n:
-        // send it off as one bulk tensor reduction and hand the staging tile back once it has been read.
-        if (n > 0) send_dq(n - 1);
-        TR(2, 3)
       }
-      if (total_steps > 0) send_dq(total_steps - 1);
-      if (lane == 0) tma_wait_group0();
-#ifdef EVO_PROF
-      prof_[14] = total_steps;
-      PROF_FLUSH(4)
-#endif
-    } else if (warp == kCW + 3) {
+      }  // lane 0
+    } else {
       // =============================== tile loader ===============================
-      // K/V of row g stay for the whole item and are replaced when the item's last dQ MMAs of that
-      // row have completed; Q, dO and the two statistics vectors of a step ride a three-deep ring.
+      // K/V of row g stay for the whole item and are replaced when the item's last MMAs that read them
+      // have completed; Q, dO and the two statistics vectors of a step ride a two-deep ring.
       const uint32_t sKV_s = smem_u32(sKV), sStage_s = smem_u32(sStage);
-      PROF_DECL
       StepT d = decode(0);
       for (int n = 0; n < total_steps; ++n) {
         const int stg = n % kStages;
         if (d.it == 0) {
           const int k = n / SPI;
-          PROF_BEGIN
           mbar_wait(kv_empty + d.g, (k & 1) ^ 1, abort_s, a.status, DEV_TIMEOUT_MMA);
-          PROF_END(0)
           if (lane == 0) {
             const uint32_t dst = sKV_s + (2 * d.g) * L::kTile;
             mbar_expect_tx(kv_full + d.g, 2 * L::kTile);
@@ -457,9 +386,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
           }
           __syncwarp();
         }
-        PROF_BEGIN
         mbar_wait(st_empty + stg, ((n / kStages) & 1) ^ 1, abort_s, a.status, DEV_TIMEOUT_MMA);
-        PROF_END(1)
         if (lane == 0) {
           const uint32_t dst = sStage_s + stg * L::kStage;
           const uint32_t bar = (st_full + stg).a;
@@ -472,22 +399,27 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
         __syncwarp();
         d = advance(d, n + 1);
       }
-      PROF_FLUSH(2)
     }
   } else {
     // =============================== compute warps ===============================
+    // Warps 0-7 work on half 0 (queries 0..63 of the tile) of every step, warps 8-15 on half 1: two
+    // groups that run half a step apart, so that while one waits (for its S^T/dP^T, for tensor
+    // memory, for its MMAs) the other has arithmetic to issue.  Warp w: keys 32*(w%4).. (its TMEM
+    // lanes), queries 32*((w/4)%2).. of its half, in two chunks of 16.
     setmaxnreg_inc<kComputeRegs>();
-    const int q4 = warp & 3;     // TMEM lane quadrant: keys 32*q4 .. 32*q4+31 of the tile
-    const int cb = warp >> 2;    // column block: queries 16*cb .. 16*cb+15 of each half
+    const int q4 = warp & 3, cb2 = (warp >> 2) & 1, H = warp >> 3;
     const int jrow = q4 * 32 + lane;
     const uint32_t t_lane = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
+    const uint32_t cS = t_lane + (H ? colS1 : colS0) + 32 * cb2, cP = t_lane + (H ? colDP1 : colDP0) + 32 * cb2;
     const float scale = a.scale;
     const float inv_r = 1.f / (float)a.R;
     const float kInf = __int_as_float(0x7f800000);
     const float c1 = scale * kLog2e;
     // 32-bit shared-window addresses: every access below stays a shared-memory instruction
-    const uint32_t sStage_s = smem_u32(sStage), sBias_s = smem_u32(sBias), sDS_s = smem_u32(sDS), sDQ_s = smem_u32(sDQ);
-    const uint32_t scratch_s = smem_u32(const_cast<uint32_t*>(scratch));
+    const uint32_t sStage_s = smem_u32(sStage), sDS_s = smem_u32(sDS);
+    const uint32_t out_s = smem_u32(sOut) + warp * L::kOutWarp;  // this warp's private staging area
+    const uint32_t brow0 = smem_u32(sBias) + (H * HT + 32 * cb2) * (BT * 4) + jrow * 4;
+    const uint32_t drow = sDS_s + H * (L::kDS / 2) + jrow * 128;
 
     // The residue mask of (b, s, key) in two halves, so that the load can be issued a step before
     // its value is needed: the raw element ...
@@ -508,54 +440,65 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       const uint16_t h16 = (uint16_t)raw;
       return to_float<T>(*reinterpret_cast<const T*>(&h16)) * kLog2e;
     };
+    // This warp's staging area is free again once its previous bulk reduction has read it.
+    auto staging_free = [&]() {
+      if (lane == 0) tma_wait_group_read0();
+      __syncwarp();
+    };
 
-    // dK, dV of row-group slot g (MSA row s of (b,h), keys j0..): TMEM -> registers -> global
+    // dK, dV of row-group slot g (MSA row s of (b,h), keys j0..): TMEM -> registers -> global.
+    // Done by the warps of half 0 (16 of the 32 columns each): they are the ones whose arrival
+    // lets the next item's first MMAs overwrite the slot.
     auto drain_dkdv = [&](int b, int h, int s, int j0, int g) {
       const int j = j0 + jrow;
-      uint32_t kr[QD], vr[QD];
-      tmem_ld<QD>(t_lane + colDK + g * DP + cb * QD, kr);
-      tmem_ld<QD>(t_lane + colDV + g * DP + cb * QD, vr);
+      uint32_t kr[16], vr[16];
+      tmem_ld16(t_lane + colDK + g * DP + cb2 * 16, kr);
+      tmem_ld16(t_lane + colDV + g * DP + cb2 * 16, vr);
       tmem_wait_ld();
-      if (j < a.R && s < a.S && cb * QD < a.D) {
-        T* kd = reinterpret_cast<T*>(a.dk) + off4(a.sdk, b, h, s, j) + cb * QD;
-        T* vd = reinterpret_cast<T*>(a.dv) + off4(a.sdv, b, h, s, j) + cb * QD;
-        uint4 pk, pv;
-        pk.x = Pack2<T>::pack(__uint_as_float(kr[0]) * scale, __uint_as_float(kr[1]) * scale);
-        pk.y = Pack2<T>::pack(__uint_as_float(kr[2]) * scale, __uint_as_float(kr[3]) * scale);
-        pk.z = Pack2<T>::pack(__uint_as_float(kr[4]) * scale, __uint_as_float(kr[5]) * scale);
-        pk.w = Pack2<T>::pack(__uint_as_float(kr[6]) * scale, __uint_as_float(kr[7]) * scale);
-        pv.x = Pack2<T>::pack(__uint_as_float(vr[0]), __uint_as_float(vr[1]));
-        pv.y = Pack2<T>::pack(__uint_as_float(vr[2]), __uint_as_float(vr[3]));
-        pv.z = Pack2<T>::pack(__uint_as_float(vr[4]), __uint_as_float(vr[5]));
-        pv.w = Pack2<T>::pack(__uint_as_float(vr[6]), __uint_as_float(vr[7]));
-        *reinterpret_cast<uint4*>(kd) = pk;
-        *reinterpret_cast<uint4*>(vd) = pv;
+      if (j < a.R && s < a.S) {
+        T* kd = reinterpret_cast<T*>(a.dk) + off4(a.sdk, b, h, s, j) + cb2 * 16;
+        T* vd = reinterpret_cast<T*>(a.dv) + off4(a.sdv, b, h, s, j) + cb2 * 16;
+#pragma unroll
+        for (int d8 = 0; d8 < 2; ++d8) {
+          if (cb2 * 16 + d8 * 8 < a.D) {
+            uint4 pk, pv;
+            pk.x = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 0]) * scale, __uint_as_float(kr[d8 * 8 + 1]) * scale);
+            pk.y = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 2]) * scale, __uint_as_float(kr[d8 * 8 + 3]) * scale);
+            pk.z = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 4]) * scale, __uint_as_float(kr[d8 * 8 + 5]) * scale);
+            pk.w = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 6]) * scale, __uint_as_float(kr[d8 * 8 + 7]) * scale);
+            pv.x = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 0]), __uint_as_float(vr[d8 * 8 + 1]));
+            pv.y = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 2]), __uint_as_float(vr[d8 * 8 + 3]));
+            pv.z = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 4]), __uint_as_float(vr[d8 * 8 + 5]));
+            pv.w = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 6]), __uint_as_float(vr[d8 * 8 + 7]));
+            *reinterpret_cast<uint4*>(kd + d8 * 8) = pk;
+            *reinterpret_cast<uint4*>(vd + d8 * 8) = pv;
+          }
+        }
       }
     };
-    // The dQ partial of step n (TMEM lanes = queries): this warp's 8 columns of its 32 query rows go
-    // into the staging tile (128-byte-swizzled rows), from where warp 18 adds it to the fp32
-    // accumulator in global memory with one bulk tensor reduction.
-    auto stage_dq = [&](int n) {
-      mbar_wait(dq_full + (n & 1), (n >> 1) & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
+    // The dQ partial of step m at position d (TMEM lanes = queries): this warp's 8 columns of its 32
+    // query rows go through its staging area ([32 rows][8 floats]) into the fp32 accumulator in global
+    // memory, as one small bulk tensor reduction that the warp issues itself.  It happens after the
+    // warp's arrival, underneath the tensor core's turnaround for its half.
+    const int colblk = 2 * H + cb2;  // the 8 dQ columns this warp drains
+    auto send_dq = [&](int m, const StepT& d) {
+      mbar_wait(dq_full + (m & 1), (m >> 1) & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
       tc_fence_after();
-      uint32_t qr[QD];
-      tmem_ld<QD>(t_lane + colDQ + (n & 1) * DP + cb * QD, qr);
+      uint32_t qr[8];
+      tmem_ld8(t_lane + colDQ + (m & 1) * DP + colblk * 8, qr);
+      staging_free();
       tmem_wait_ld();
-      mbar_wait(dqs_empty, (n & 1) ^ 1, abort_s, a.status, DEV_TIMEOUT_SYNC);  // the previous partial has left
-      const uint32_t dst = sDQ_s + jrow * 128;
-#pragma unroll
-      for (int c = 0; c < QD / 4; ++c)
-        sts_v4(dst + (((cb * (QD / 4) + c) ^ (jrow & 7)) << 4), qr[c * 4], qr[c * 4 + 1], qr[c * 4 + 2], qr[c * 4 + 3]);
+      sts_v4(out_s + lane * 32, qr[0], qr[1], qr[2], qr[3]);
+      sts_v4(out_s + lane * 32 + 16, qr[4], qr[5], qr[6], qr[7]);
       fence_async_shared();
       __syncwarp();
-      if (lane == 0) mbar_arrive(dqs_full);
+      if (lane == 0 && d.s < a.S && colblk * 8 < a.D) {
+        tma_reduce_add_3d_s(&tmDQ, out_s, colblk * 8, d.it * BT + q4 * 32, (d.b * a.H + d.h) * a.S + d.s);
+        tma_commit_group();
+      }
     };
 
-    PROF_DECL
-#ifdef EVO_PROF
-    const long long tl0 = clock64();
-#endif
-    StepT cur = decode(0);
+    StepT cur = decode(0), prv = cur;
     uint32_t mraw = mask_fetch(cur.b, cur.s, cur.j0 + jrow, total_steps > 0);
     int pb = 0, ph = 0, ps0 = 0, pj0 = 0;  // the item whose dK/dV still sit in TMEM
     float bacc[32];
@@ -571,39 +514,26 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       const int stg = n % kStages;
       const uint32_t vec_s = sStage_s + stg * L::kStage + 2 * L::kTile;
       const bool last_of_group = (g == G - 1);
-      if (warp == 0) { TR(0, 0) } else if (warp == 9) { TR(3, 0) }
+      if (warp == 0) { TR(0, 0) } else if (warp == 8) { TR(3, 0) }
       // the statistics vectors of this step are read with ordinary loads: observe their arrival here
-      PROF_BEGIN
       mbar_wait(st_full + stg, (n / kStages) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
-      PROF_END(0)
-      if (warp == 0) { TR(0, 1) } else if (warp == 9) { TR(3, 1) }
-
-      auto mini = [&](auto hc) {
-        constexpr int H = decltype(hc)::value;
-        constexpr int cS = H ? colS1 : colS0, cP = H ? colDP1 : colDP0;
-        PROF_BEGIN
-        mbar_wait(sd_full + H, n & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
-        PROF_END(1 + H)
-        if (warp == 0) { TR(0, 2 + H * 10) } else if (warp == 9) { TR(3, 2 + H * 10) }
-        tc_fence_after();
+      mbar_wait(sd_full + H, n & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
+      tc_fence_after();
+      if (warp == 0) { TR(0, 1) } else if (warp == 8) { TR(3, 1) }
+      if (has_bias && g == 0) mbar_wait(b_full + H, (n / G) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
+      // a row whose keys are all dropped has nl = +inf for every query (the mask row is shared by
+      // all queries of the MSA row): the whole step is uniform, P = 1/N_res, dS = 0
+      const bool deadstep = (lds_f32(vec_s) == kInf);
+      uint32_t dk[16];
+#pragma unroll
+      for (int sub = 0; sub < 2; ++sub) {
         uint32_t sr[16], dr[16];
-        tmem_ld16(t_lane + cS + 16 * cb, sr);
-        tmem_ld16(t_lane + cP + 16 * cb, dr);
-        PROF_BEGIN
-        if (has_bias && g == 0) mbar_wait(b_full + H, (n / G) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
-        PROF_END(3)
-        if (warp == 0) { TR(0, 3 + H * 10) } else if (warp == 9) { TR(3, 3 + H * 10) }
-        // a row whose keys are all dropped has nl = +inf for every query (the mask row is shared by
-        // all queries of the MSA row): the whole step is uniform, P = 1/N_res, dS = 0
-        const bool deadstep = (lds_f32(vec_s) == kInf);
-        const uint32_t vnl = vec_s + (H * HT + 16 * cb) * 4, vdl = vnl + BT * 4;
-        const uint32_t brow = sBias_s + (H * HT + 16 * cb) * (BT * 4) + jrow * 4;
-        PROF_BEGIN
+        tmem_ld16(cS + 16 * sub, sr);
+        tmem_ld16(cP + 16 * sub, dr);
+        const uint32_t vnl = vec_s + (H * HT + 32 * cb2 + 16 * sub) * 4, vdl = vnl + BT * 4;
+        const uint32_t brow = brow0 + (16 * sub) * (BT * 4);
         tmem_wait_ld();
-        PROF_END(4)
-        if (warp == 0) { TR(0, 4 + H * 10) } else if (warp == 9) { TR(3, 4 + H * 10) }
-        uint32_t pk[8], dk[8];
-        PROF_BEGIN
+        uint32_t pk[8];
         if (!deadstep) {
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
@@ -619,92 +549,86 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               // x = S*(scale*log2e) + (bias*log2e - lse*log2e) + mask
-              float x = fmaf(__uint_as_float(sr[4 * c4 + u]), c1, t[u]);
-              x += mj;
+              const float x = fmaf(__uint_as_float(sr[4 * c4 + u]), c1, t[u]) + mj;
               p[u] = ex2(x);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               // dS = P (dP - delta); d_bias_acc += dS
               ds[u] = p[u] * (__uint_as_float(dr[4 * c4 + u]) - de[u]);
-              bacc[H * 16 + 4 * c4 + u] += ds[u];
+              bacc[sub * 16 + 4 * c4 + u] += ds[u];
             }
             pk[2 * c4] = Pack2<T>::pack(p[0], p[1]);
             pk[2 * c4 + 1] = Pack2<T>::pack(p[2], p[3]);
-            dk[2 * c4] = Pack2<T>::pack(ds[0], ds[1]);
-            dk[2 * c4 + 1] = Pack2<T>::pack(ds[2], ds[3]);
+            dk[sub * 8 + 2 * c4] = Pack2<T>::pack(ds[0], ds[1]);
+            dk[sub * 8 + 2 * c4 + 1] = Pack2<T>::pack(ds[2], ds[3]);
           }
         } else {
           const float pu = (cur.j0 + jrow < a.R) ? inv_r : 0.f;
           const uint32_t w = Pack2<T>::pack(pu, pu);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) { pk[e] = w; dk[e] = 0u; }  // replaced scores are constants: dS = 0
+          for (int e = 0; e < 8; ++e) { pk[e] = w; dk[sub * 8 + e] = 0u; }  // replaced scores are constants: dS = 0
         }
         // P^T and dS^T, two 16-bit values per column, over the columns this thread has just read:
         // the A operands of the dV and dK MMAs (16 queries = 8 packed columns each)
-        PROF_END(5)
-        if (warp == 0) { TR(0, 5 + H * 10) } else if (warp == 9) { TR(3, 5 + H * 10) }
-        tmem_st8(t_lane + cS + 16 * cb, pk);
-        tmem_st8(t_lane + cP + 16 * cb, dk);
-        // dS^T -> shared memory, [key][query] rows of 128 bytes per half, 128-byte swizzle
-        PROF_BEGIN
-        if (H == 0) mbar_wait(ds_empty, (n & 1) ^ 1, abort_s, a.status, DEV_TIMEOUT_MMA);
-        PROF_END(6)
-        if (warp == 0) { TR(0, 6 + H * 10) } else if (warp == 9) { TR(3, 6 + H * 10) }
-        {
-          const uint32_t drow = sDS_s + H * (L::kDS / 2) + jrow * 128;
-          sts_v4(drow + (((2 * cb) ^ (jrow & 7)) << 4), dk[0], dk[1], dk[2], dk[3]);
-          sts_v4(drow + (((2 * cb + 1) ^ (jrow & 7)) << 4), dk[4], dk[5], dk[6], dk[7]);
-        }
-        if (has_bias && last_of_group) {
-          if (flush_dbias) {
-            // this thread's 16 d_bias values go where their bias values were; warp 18 adds the
-            // half to d_bias in global memory before it loads the next tile over it
+        tmem_st8(cS + 16 * sub, pk);
+        tmem_st8(cP + 16 * sub, *reinterpret_cast<uint32_t(*)[8]>(&dk[sub * 8]));
+        if (flush_dbias && last_of_group) {
+          // The group's last row: this thread's 16 d_bias values of the chunk (one key, 16 queries) go
+          // through the warp's staging area ([16 queries][32 keys]) and are added to d_bias in global
+          // memory by a bulk tensor reduction that the warp issues itself.
+          staging_free();
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              sts_f32(brow + c * (BT * 4), bacc[H * 16 + c]);
-              bacc[H * 16 + c] = 0.f;
-            }
-          } else {
-            // hand the half back only after the loads from it have returned (an mbarrier arrival
-            // does not wait for shared loads that are still queued)
-            sts_u32(scratch_s, pk[0] ^ pk[7]);
+          for (int c = 0; c < 16; ++c) {
+            sts_f32(out_s + c * 128 + lane * 4, bacc[sub * 16 + c]);
+            bacc[sub * 16 + c] = 0.f;
+          }
+          fence_async_shared();
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_4d_s(&tmDB, out_s, cur.j0 + q4 * 32, cur.it * BT + H * HT + 32 * cb2 + 16 * sub, cur.h, cur.b);
+            tma_commit_group();
           }
         }
-        if (H == 0 && cur.it == 0 && n >= SPI) drain_dkdv(pb, ph, ps0 + g, pj0, g);  // before this step's MMAs overwrite it
-        if (warp == 0) { TR(0, 7 + H * 10) } else if (warp == 9) { TR(3, 7 + H * 10) }
-        PROF_BEGIN
-        tmem_wait_st();
-        tc_fence_before();
-        fence_async_shared();
-        __syncwarp();
-        PROF_END(7)
-        if (warp == 0) { TR(0, 8 + H * 10) } else if (warp == 9) { TR(3, 8 + H * 10) }
-        if (lane == 0) {
-          mbar_arrive(cdone + H);
-          if (has_bias && last_of_group) mbar_arrive(b_done + H);
-        }
-        if (warp == 0) { TR(0, 9 + H * 10) } else if (warp == 9) { TR(3, 9 + H * 10) }
-      };
-      mini(std::integral_constant<int, 0>{});
-      mini(std::integral_constant<int, 1>{});
-      PROF_BEGIN
-      if (n > 0) stage_dq(n - 1);  // its MMAs ran underneath this step
-      PROF_END(8)
-      if (warp == 0) { TR(0, 22) } else if (warp == 9) { TR(3, 22) }
+      }
+      // P^T and dS^T are in tensor memory: the dV / dK MMAs of this half may go
+      if (H == 0 && cur.it == 0 && n >= SPI) drain_dkdv(pb, ph, ps0 + g, pj0, g);  // before those MMAs overwrite it
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(cdone + H);
+      if (warp == 0) { TR(0, 10) } else if (warp == 8) { TR(3, 10) }
+      // dS^T -> shared memory, [key][query] rows of 128 bytes per half, 128-byte swizzle; the tile is
+      // free once the dQ MMAs of the previous step have read it
+      mbar_wait(ds_empty, (n & 1) ^ 1, abort_s, a.status, DEV_TIMEOUT_MMA);
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        sts_v4(drow + (((4 * cb2 + c) ^ (jrow & 7)) << 4), dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
+      fence_async_shared();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(sdone + H);
+        if (has_bias && last_of_group) mbar_arrive(b_done + H);
+      }
+      if (warp == 0) { TR(0, 11) } else if (warp == 8) { TR(3, 11) }
+      if (n > 0) send_dq(n - 1, prv);  // its MMAs ran underneath this step
+      if (warp == 0) { TR(0, 12) } else if (warp == 8) { TR(3, 12) }
       if (cur.it == NT - 1 && last_of_group) { pb = cur.b; ph = cur.h; ps0 = cur.s - g; pj0 = cur.j0; }
+      prv = cur;
       cur = nxt;
     }
 
-#ifdef EVO_PROF
-    prof_[15] = clock64() - tl0; prof_[14] = total_steps;
-    if (warp == 0) { PROF_FLUSH(0) }
-    if (warp == 15) { PROF_FLUSH(3) }
-#endif
     if (total_steps > 0) {
-      stage_dq(total_steps - 1);  // also the point where every MMA of this CTA has completed
-      for (int g = 0; g < G; ++g) drain_dkdv(pb, ph, ps0 + g, pj0, g);
+      send_dq(total_steps - 1, prv);
+      if (H == 0) {
+        // every dV / dK MMA of this CTA has completed once the last step's tile stage has been released
+        const int last = total_steps - 1;
+        mbar_wait(st_empty + (last % kStages), (last / kStages) & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
+        tc_fence_after();
+        for (int g = 0; g < G; ++g) drain_dkdv(pb, ph, ps0 + g, pj0, g);
+      }
     }
+    if (lane == 0) tma_wait_group0();  // this warp's reductions have completed before the CTA may exit
   }
 
   if (*abort_flag) {
@@ -736,7 +660,7 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (!make_qkv_map(&tk, a.k, a.sk, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tv, a.v, a.sv, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tdo, a.d_o, a.sdo, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
-  if (!make_rows_f32_map(&tdq, dq_acc, a.D, a.R, (long long)a.B * a.H * a.S, DP, BT)) return EVOATTN_ERR_CUDA;
+  if (!make_rows_f32_plain_map(&tdq, dq_acc, a.D, a.R, (long long)a.B * a.H * a.S, 8, 32)) return EVOATTN_ERR_CUDA;
   if (!make_stats_map(&tnl, nl, a.B * a.H, a.S, a.R, BT)) return EVOATTN_ERR_CUDA;
   if (!make_stats_map(&tdl, a.delta, a.B * a.H, a.S, a.R, BT)) return EVOATTN_ERR_CUDA;
   tb = tq;
@@ -744,12 +668,11 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (a.bias) {
     if (!make_bias_plain_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, HT, BT)) return EVOATTN_ERR_CUDA;
     const Str3 dense{(long long)a.H * a.R * a.R, (long long)a.R * a.R, (long long)a.R};
-    if (a.dbias && !make_bias_plain_map(&tdb, a.dbias, dense, a.B, a.H, a.R, HT, BT)) return EVOATTN_ERR_CUDA;
+    if (a.dbias && !make_bias_plain_map(&tdb, a.dbias, dense, a.B, a.H, a.R, 16, 32)) return EVOATTN_ERR_CUDA;
   }
-  if (cudaMemsetAsync(dq_acc, 0, dq_bytes, st) != cudaSuccess) return EVOATTN_ERR_CUDA;
   if (a.dbias && cudaMemsetAsync(a.dbias, 0, (size_t)a.B * a.H * a.R * a.R * sizeof(float), st) != cudaSuccess)
     return EVOATTN_ERR_CUDA;
-  prep_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(a, nl);
+  prep_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(a, nl, dq_acc);
 
   const int NT = (a.R + BT - 1) / BT;
   const long long items = (long long)a.B * a.H * NT * ((a.S + G - 1) / G);
@@ -778,9 +701,6 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
 
 #ifdef EVO_TRACE
 extern "C" int evoattn_debug_trace(void* dst, size_t bytes) { return (int)cudaMemcpyFromSymbol(dst, g_trace, bytes); }
-#endif
-#ifdef EVO_PROF
-extern "C" int evoattn_debug_prof(void* dst, size_t bytes) { return (int)cudaMemcpyFromSymbol(dst, g_prof, bytes); }
 #endif
 
 size_t sm100_bwdt_workspace_bytes(const Args& a) {

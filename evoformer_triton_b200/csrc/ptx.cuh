@@ -538,6 +538,76 @@ __device__ __forceinline__ void tma_reduce_add_3d_s(const CUtensorMap* map, uint
       : "memory");
 }
 
+// ---------------------------------------------------------------- MMA groups in one statement
+// The compiler spends dozens of instructions on every separately written tcgen05.mma (descriptor
+// assembly, moves into uniform registers).  A warp that issues many small MMAs next to busy
+// arithmetic warps is bound by that, so the fixed groups of the backward are written out: operands
+// in, a handful of adds, the MMAs.  All are issued by the calling thread (call from one lane).
+// Four D[tmem] (+)= A[tmem] * B[smem] with A advancing 16 columns and B advancing `b_step` descriptor
+// units per MMA; the first overwrites D unless `acc_first`.
+__device__ __forceinline__ void mma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t b_step,
+                                          uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 d0, d1, d2, d3;\n\t.reg .b32 a1, a2, a3, l1, l2, l3;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "add.u32 l1, %2, %4;\n\tadd.u32 l2, l1, %4;\n\tadd.u32 l3, l2, %4;\n\t"
+      "add.u32 a1, %1, 16;\n\tadd.u32 a2, %1, 32;\n\tadd.u32 a3, %1, 48;\n\t"
+      "mov.b64 d0, {%2, %3};\n\tmov.b64 d1, {l1, %3};\n\tmov.b64 d2, {l2, %3};\n\tmov.b64 d3, {l3, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d0, %5, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], d1, %5, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], d2, %5, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], d3, %5, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(b_step), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+// Two D[tmem] = A[smem] * B[smem] over two K slices (descriptors advance by `k_step` units), then a
+// commit to `bar` (and to `bar2` if non-zero).
+__device__ __forceinline__ void mma_ss_x2_commit(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t k_step,
+                                                 uint32_t idesc, uint32_t bar, uint32_t bar2) {
+  asm volatile(
+      "{\n\t.reg .pred f, t, c;\n\t.reg .b64 a0, a1, b0, b1;\n\t.reg .b32 x, y;\n\t"
+      "setp.ne.b32 f, 0, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "setp.ne.b32 c, %7, 0;\n\t"
+      "add.u32 x, %1, %4;\n\tadd.u32 y, %2, %4;\n\t"
+      "mov.b64 a0, {%1, %3};\n\tmov.b64 a1, {x, %3};\n\tmov.b64 b0, {%2, %3};\n\tmov.b64 b1, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a0, b0, %5, f;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %5, t;\n\t"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+      "@c tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(k_step), "r"(idesc), "r"(bar), "r"(bar2)
+      : "memory");
+}
+// Eight D[tmem] = A[smem] * B[smem] (the first overwrites), A and B descriptors advancing by
+// `a_step` / `b_step` units per MMA, different high words.
+__device__ __forceinline__ void mma_ss_x8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t a_step, uint32_t b_lo,
+                                          uint32_t b_hi, uint32_t b_step, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t.reg .b32 x, y;\n\t"
+      "setp.ne.b32 p, 0, 0;\n\t"
+      "mov.u32 x, %1;\n\tmov.u32 y, %4;\n\t"
+      "mov.b64 da, {x, %2};\n\tmov.b64 db, {y, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "add.u32 x, x, %3;\n\tadd.u32 y, y, %6;\n\tmov.b64 da, {x, %2};\n\tmov.b64 db, {y, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+      "add.u32 x, x, %3;\n\tadd.u32 y, y, %6;\n\tmov.b64 da, {x, %2};\n\tmov.b64 db, {y, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+      "add.u32 x, x, %3;\n\tadd.u32 y, y, %6;\n\tmov.b64 da, {x, %2};\n\tmov.b64 db, {y, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+      "add.u32 x, x, %3;\n\tadd.u32 y, y, %6;\n\tmov.b64 da, {x, %2};\n\tmov.b64 db, {y, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+      "add.u32 x, x, %3;\n\tadd.u32 y, y, %6;\n\tmov.b64 da, {x, %2};\n\tmov.b64 db, {y, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+      "add.u32 x, x, %3;\n\tadd.u32 y, y, %6;\n\tmov.b64 da, {x, %2};\n\tmov.b64 db, {y, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+      "add.u32 x, x, %3;\n\tadd.u32 y, y, %6;\n\tmov.b64 da, {x, %2};\n\tmov.b64 db, {y, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(a_step), "r"(b_lo), "r"(b_hi), "r"(b_step), "r"(idesc)
+      : "memory");
+}
+
 // Non-blocking arrival on a named barrier that other threads wait on with named_bar_sync.
 __device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

@@ -79,6 +79,19 @@ bool make_rows_f32_map(CUtensorMap* out, const float* base, int D, int R, long l
   return r == CUDA_SUCCESS;
 }
 
+bool make_rows_f32_plain_map(CUtensorMap* out, const float* base, int D, int R, long long slabs, int box_d, int box_r) {
+  std::call_once(g_once, resolve);
+  if (!g_encode) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)R, (cuuint64_t)slabs};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 4, (cuuint64_t)D * 4 * (cuuint64_t)R};
+  cuuint32_t box[3] = {(cuuint32_t)box_d, (cuuint32_t)box_r, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 bool make_bias_plain_map(CUtensorMap* out, const float* base, const Str3& st, int B, int H, int R, int box_i,
                          int box_j) {
   std::call_once(g_once, resolve);

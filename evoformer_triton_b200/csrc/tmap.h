@@ -22,6 +22,8 @@ bool make_bias_map(CUtensorMap* out, const float* base, const Str3& stride_elems
 // Contiguous fp32 [slabs, R, D] (the dQ accumulator: one slab per (b,h,s)) as a 3-D map
 // (D, R, slabs) with box (box_d, box_r, 1); rows and columns beyond R and D are clipped.
 bool make_rows_f32_map(CUtensorMap* out, const float* base, int D, int R, long long slabs, int box_d, int box_r);
+// The same tensor with an unswizzled box (rows of box_d floats land back to back in shared memory).
+bool make_rows_f32_plain_map(CUtensorMap* out, const float* base, int D, int R, long long slabs, int box_d, int box_r);
 
 // fp32 [B,H,R,R] pair bias (or its dense gradient) as a 4-D map (R_j, R_i, H, B) with an
 // unswizzled box (box_j, box_i, 1, 1): rows of box_j floats land back to back in shared memory.
