@@ -179,6 +179,9 @@ def main():
     ap.add_argument("--cpu-baseline-rows", type=int, default=128)
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every rank holds the workload's N_seq rows of its own; strong: the workload's rows are split over the ranks")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="sum of d(pair_bias) over the ranks: this package's peer-memory kernel (falls back to NCCL "
+                         "if peer mapping is unavailable) or an NCCL all-reduce")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -216,13 +219,30 @@ def main():
     Q, K, V, dO = x["Q"], x["K"], x["V"], x["dO"]
     mask, bias = x["res_mask"], x["pair_bias"]
     Q.requires_grad_(); K.requires_grad_(); V.requires_grad_(); bias.requires_grad_()
+    reducer, collective = None, "none"
+    if world > 1:
+        collective = "NCCL all-reduce of d(pair_bias) inside the step"
+        if args.collective == "peer":
+            from evoformer_triton_b200.sharding import PeerReducer
+            ok = torch.ones(1, device=dev)
+            try:
+                reducer = PeerReducer(bias.numel(), dev)
+            except RuntimeError as e:  # no peer mapping on this box: every rank must agree on the fallback
+                ok.zero_()
+                if rank == 0:
+                    print(f"peer-memory reducer unavailable ({e}); using NCCL", file=sys.stderr)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0:
+                reducer = None
+            else:
+                collective = "peer-memory all-reduce of d(pair_bias) (own kernel over NVLink) inside the step"
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB of L2
 
     def zero_grads():
         Q.grad = K.grad = V.grad = bias.grad = None
 
     def step(q=Q, k=K, v=V, m=mask, b=bias, g=dO):
-        out = sharded_evoformer_attention(evo.EvoformerAttention.apply, q, k, v, m, b)
+        out = sharded_evoformer_attention(evo.EvoformerAttention.apply, q, k, v, m, b, peer_reducer=reducer)
         out.backward(g)
         return out
 
@@ -400,7 +420,7 @@ def main():
             "config": {"workload": describe(w_job if args.scaling == "strong" else w), "rows_per_gpu": w.S,
                        "global_rows": w.S * world,
                        "l2": "256 MB buffer written between timed steps",
-                       "collective": "NCCL all-reduce of d(pair_bias) inside the step" if world > 1 else "none",
+                       "collective": collective,
                        "paths": {k: {0: "none", 1: "cuda-core", 2: "tcgen05"}[v] for k, v in paths.items()}},
             "frac_of_bf16_peak": value / (peaks["tflops"] * world),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,

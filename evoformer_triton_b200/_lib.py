@@ -17,6 +17,8 @@ PATH_NONE, PATH_GENERIC, PATH_TCGEN05 = 0, 1, 2
 SYMBOLS = (
     "evoattn_abi_version", "evoattn_strerror", "evoattn_fwd", "evoattn_bwd_workspace_bytes",
     "evoattn_bwd", "evoattn_bwd_static_scratch", "evoattn_last_path", "evoattn_last_launch_count",
+    "evoattn_peer_flag_bytes", "evoattn_peer_buffer_create", "evoattn_peer_buffer_open",
+    "evoattn_peer_buffer_close", "evoattn_peer_buffer_destroy", "evoattn_peer_allreduce_f32",
 )
 STATIC_SCRATCH_BYTES = 64 << 20
 
@@ -50,6 +52,15 @@ class BwdParams(C.Structure):
     ]
 
 
+class PeerAllReduceParams(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32),
+        ("bufs", C.POINTER(C.c_void_p)), ("flags", C.POINTER(C.c_void_p)),
+        ("count", C.c_uint64), ("epoch", C.c_uint32),
+        ("status", C.c_void_p),
+    ]
+
+
 _lib = None
 _lock = threading.Lock()
 
@@ -80,6 +91,17 @@ def load() -> C.CDLL:
         lib.evoattn_bwd_static_scratch.argtypes = [C.POINTER(BwdParams), C.c_void_p]
         lib.evoattn_last_path.restype = C.c_int
         lib.evoattn_last_launch_count.restype = C.c_int
+        lib.evoattn_peer_flag_bytes.restype = C.c_size_t
+        lib.evoattn_peer_buffer_create.restype = C.c_int
+        lib.evoattn_peer_buffer_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]
+        lib.evoattn_peer_buffer_open.restype = C.c_int
+        lib.evoattn_peer_buffer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+        lib.evoattn_peer_buffer_close.restype = C.c_int
+        lib.evoattn_peer_buffer_close.argtypes = [C.c_void_p]
+        lib.evoattn_peer_buffer_destroy.restype = C.c_int
+        lib.evoattn_peer_buffer_destroy.argtypes = [C.c_void_p]
+        lib.evoattn_peer_allreduce_f32.restype = C.c_int
+        lib.evoattn_peer_allreduce_f32.argtypes = [C.POINTER(PeerAllReduceParams), C.c_void_p]
         if lib.evoattn_abi_version() != ABI_VERSION:
             raise RuntimeError("libevoattn.so ABI version mismatch; rebuild it")
         _lib = lib

@@ -131,7 +131,7 @@ def attention_forward(q, k, v, mask, bias, scale):
     return o, lse
 
 
-def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True):
+def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True, dbias_out=None):
     """Raw backward on attention-view tensors.  Returns (dq, dk, dv, dbias fp32 or None).
     ``want_dbias=False`` skips d(pair_bias) (its reductions are the backward's largest stream
     of writes; speed_benchmark.py:68 builds the bias without ``requires_grad``)."""
@@ -142,7 +142,9 @@ def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True)
     dv = torch.empty_like(dq)
     dbias = None
     if bias is not None and want_dbias:
-        dbias = torch.empty((B, H, R, R), dtype=torch.float32, device=q.device)
+        # (``dbias_out``: caller-provided fp32 storage, e.g. a buffer peers can reach)
+        dbias = dbias_out.view(B, H, R, R) if dbias_out is not None else \
+            torch.empty((B, H, R, R), dtype=torch.float32, device=q.device)
     p = _lib.BwdParams()
     _fill_fwd(p.fwd, q, k, v, o, lse, mask, bias, scale)
     p.d_o, p.dq, p.dk, p.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
@@ -163,13 +165,15 @@ _pending = threading.local()
 
 
 @contextlib.contextmanager
-def pair_bias_grad_summed_over(group):
+def pair_bias_grad_summed_over(group, peer_reducer=None):
     """Calls of the op made inside this context sum their d(pair_bias) over the ranks of
     ``group`` (``None`` = the default process group) in backward: the fp32 sum over the local
     MSA rows is all-reduced as it leaves the kernel, before the single cast to the bias dtype.
-    Used by :func:`evoformer_triton_b200.sharding.sharded_evoformer_attention`."""
+    With ``peer_reducer`` (:class:`evoformer_triton_b200.sharding.PeerReducer`) the kernel writes
+    into peer-mapped memory and the sum runs over NVLink in this package's own kernel instead of
+    NCCL.  Used by :func:`evoformer_triton_b200.sharding.sharded_evoformer_attention`."""
     prev = getattr(_pending, "group", None)
-    _pending.group = (group,)
+    _pending.group = (group, peer_reducer)
     try:
         yield
     finally:
@@ -222,16 +226,22 @@ class _EvoformerAttentionBase(torch.autograd.Function):
         if d_o.dtype != q.dtype:
             d_o = d_o.to(q.dtype)
         want_dbias = bias is not None and ctx.needs_input_grad[4]
+        reducer = ctx.reduce_group[1] if (ctx.reduce_group is not None and want_dbias) else None
+        dbias_out = reducer.buffer(bias.numel()) if reducer is not None else None
         dq, dk, dv, dbias = attention_backward(q, k, v, o, lse, mask, bias, ctx.softmax_scale, d_o,
-                                               want_dbias=want_dbias)
+                                               want_dbias=want_dbias, dbias_out=dbias_out)
         d_pair_bias = None
         if dbias is not None:
             dtype, shape = ctx.bias_meta
-            if ctx.reduce_group is not None:  # N_seq is sharded: the other ranks' rows belong to the sum
+            if reducer is not None:  # N_seq is sharded: the other ranks' rows belong to the sum
+                reducer.allreduce_(bias.numel())
+            elif ctx.reduce_group is not None:
                 import torch.distributed as dist
                 dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=ctx.reduce_group[0])
             # the sum over N_seq stays in fp32 until this single cast (evoformer.py:860 casts to dO's dtype)
             d_pair_bias = dbias.reshape(shape).to(dtype)
+            if reducer is not None and d_pair_bias.data_ptr() == dbias.data_ptr():
+                d_pair_bias = d_pair_bias.clone()  # the exchange buffer is reused by the next call
         return _unview(dq, cls.layout), _unview(dk, cls.layout), _unview(dv, cls.layout), None, d_pair_bias
 
 

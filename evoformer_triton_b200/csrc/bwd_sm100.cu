@@ -1056,11 +1056,7 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       return EVOATTN_ERR_CUDA;
     const long long ctas = items < sms ? items : sms;
-    if (DP == 32) {
-      const int rc = launch_sm100_bwd16(std::is_same<T, __nv_bfloat16>::value ? EVOATTN_BF16 : EVOATTN_FP16, a, dq_acc,
-                                        items, (int)ctas, tq, tk, tv, tdo, tb, tdb, st);
-      if (rc != EVOATTN_OK) return rc;
-    } else {
+    {
       auto kern = add ? evo_bwd_ws_kernel<T, DP, MASK_ADD> : evo_bwd_ws_kernel<T, DP, MASK_MIN>;
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)W::bytes) != cudaSuccess)
         return EVOATTN_ERR_CUDA;
@@ -1082,13 +1078,9 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
 template <class T>
 int launch_d(const Args& a, void* ws, size_t ws_bytes, cudaStream_t st, int* launches) {
   if (a.D <= 16) return launch_t<T, 16>(a, ws, ws_bytes, st, launches);
-#ifndef EVO_USE_BWD16
-  if (a.D <= 32)
+  if (a.D <= 32)  // the kernel with transposed score tiles (bwdt_sm100.cu)
     return launch_sm100_bwdt(std::is_same<T, __nv_bfloat16>::value ? EVOATTN_BF16 : EVOATTN_FP16, a, ws, ws_bytes, st,
                              launches);
-#else
-  if (a.D <= 32) return launch_t<T, 32>(a, ws, ws_bytes, st, launches);
-#endif
   return launch_t<T, 64>(a, ws, ws_bytes, st, launches);
 }
 
@@ -1102,9 +1094,7 @@ bool sm100_bwd_supported(int dtype, const Args& a) {
 }
 
 size_t sm100_bwd_workspace_bytes(int, const Args& a) {
-#ifndef EVO_USE_BWD16
   if (a.D > 16 && a.D <= 32) return sm100_bwdt_workspace_bytes(a);
-#endif
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;
   return align_up(rows * sizeof(float), 256) + rows * a.D * sizeof(float);
 }

@@ -565,6 +565,7 @@ bool sm100_fwd_supported(int dtype, const Args& a) {
   if (a.bias) {
     if ((reinterpret_cast<uintptr_t>(a.bias) & 15) != 0) return false;
     if ((a.sbias.a * 4) % 16 || (a.sbias.b * 4) % 16 || (a.sbias.c * 4) % 16) return false;
+    if (a.R % 4 != 0) return false;  // rows of the bias tensor map are whole 16-byte pieces
   }
   if ((long long)a.B * a.H * a.S * ((a.R + BM - 1) / BM) > 2147483647LL) return false;
   return true;

@@ -21,13 +21,6 @@ size_t sm100_bwd_workspace_bytes(int dtype, const Args& a);
 int launch_sm100_bwd(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
                      int* launches);
 
-// The fused backward kernel with sixteen compute warps (bwd16_sm100.cu; head dimension padded to
-// 32): work list of `items` items on `ctas` persistent CTAs, tensor maps as built by
-// launch_sm100_bwd for its own kernel.
-int launch_sm100_bwd16(int dtype, const Args& a, float* dq_acc, long long items, int ctas, const CUtensorMap& tq,
-                       const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tb,
-                       const CUtensorMap& tdb, cudaStream_t st);
-
 // The fused backward with transposed score tiles (bwdt_sm100.cu; head dimensions 17..32).
 size_t sm100_bwdt_workspace_bytes(const Args& a);
 int launch_sm100_bwdt(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,

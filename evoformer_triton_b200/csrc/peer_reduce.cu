@@ -1,0 +1,164 @@
+// Sum of one fp32 buffer over the GPUs of a node through peer memory (NVLink / NVSwitch), in
+// place: the d(pair_bias) exchange of the N_seq-sharded op.
+//
+// The reference is a single-GPU program (its d_pair_bias is complete after the local atomics of
+// dsevoformer-triton/evoformer.py:458 and the cast at :860); sharding the MSA rows over GPUs adds
+// one sum over ranks, and for the few megabytes involved a library all-reduce costs more in launch
+// and protocol latency than in bytes.  Here every rank maps every other rank's buffer (CUDA IPC)
+// and one kernel per rank does a two-shot all-reduce with plain peer loads and stores:
+//   barrier  - all ranks have finished writing their local sums
+//   rank r sums slice r over the ranks in a fixed order (so every rank ends with the same bits)
+//   and stores the result into slice r of every rank's buffer
+//   barrier  - all slices have landed everywhere
+// Barriers are per thread block (block b of every rank meets block b of the others) through flag
+// words in each rank's own memory that peers write with system-scope release stores; flags carry
+// an epoch that grows with every call, so they are never reset.  Every wait is bounded: when it
+// runs out the kernel records a code in the status word and goes on without waiting (the result
+// is then invalid, the GPU stays usable).  No multicast loads, no multimem.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace evo {
+namespace {
+
+constexpr int kMaxPeers = 8;
+constexpr int kBlocks = 32;
+constexpr int kThreads = 512;
+constexpr long long kPeerWaitCycles = 4000000000LL;  // about two seconds
+
+struct PeerArgs {
+  float* buf[kMaxPeers];
+  uint32_t* flag[kMaxPeers];  // each rank's pad: [2 barriers][kBlocks][kMaxPeers] words
+  int world, rank;
+  unsigned long long count;
+  uint32_t epoch;
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_peer_v4(const float4* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_peer_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const PeerArgs p) {
+  const int b = blockIdx.x, tid = threadIdx.x;
+  // meet block b of every other rank: tell them, then wait for them (thread q handles rank q)
+  auto barrier = [&](int which, int code) {
+    __syncthreads();
+    if (tid < p.world) {
+      __threadfence_system();
+      st_release_sys(p.flag[tid] + (which * kBlocks + b) * kMaxPeers + p.rank, p.epoch);
+      const uint32_t* mine = p.flag[p.rank] + (which * kBlocks + b) * kMaxPeers + tid;
+      const long long t0 = clock64();
+      // epochs only grow: a value at or beyond this call's epoch means that rank has arrived
+      while ((int32_t)(ld_acquire_sys(mine) - p.epoch) < 0) {
+        if (clock64() - t0 > kPeerWaitCycles) {
+          if (p.status) atomicCAS(p.status, 0, code);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  };
+
+  barrier(0, DEV_TIMEOUT_SYNC);
+
+  const unsigned long long n4 = p.count / 4;
+  const unsigned long long lo = n4 * p.rank / p.world, hi = n4 * (p.rank + 1) / p.world;
+  for (unsigned long long i = lo + (unsigned long long)b * kThreads + tid; i < hi; i += (unsigned long long)kBlocks * kThreads) {
+    float4 v[kMaxPeers];
+#pragma unroll
+    for (int q = 0; q < kMaxPeers; ++q)
+      if (q < p.world) v[q] = ld_peer_v4(reinterpret_cast<const float4*>(p.buf[q]) + i);
+    float4 acc = v[0];
+#pragma unroll
+    for (int q = 1; q < kMaxPeers; ++q)
+      if (q < p.world) { acc.x += v[q].x; acc.y += v[q].y; acc.z += v[q].z; acc.w += v[q].w; }
+#pragma unroll
+    for (int q = 0; q < kMaxPeers; ++q)
+      if (q < p.world) reinterpret_cast<float4*>(p.buf[q])[i] = acc;
+  }
+  if (p.rank == 0 && b == 0 && tid < (int)(p.count & 3)) {  // the last count % 4 elements
+    const unsigned long long i = n4 * 4 + tid;
+    float acc = 0.f;
+    for (int q = 0; q < p.world; ++q) acc += ld_peer_f32(p.buf[q] + i);
+    for (int q = 0; q < p.world; ++q) p.buf[q][i] = acc;
+  }
+
+  barrier(1, DEV_TIMEOUT_SYNC);
+}
+
+}  // namespace
+}  // namespace evo
+
+extern "C" {
+
+size_t evoattn_peer_flag_bytes(void) { return (size_t)2 * evo::kBlocks * evo::kMaxPeers * sizeof(uint32_t); }
+
+int evoattn_peer_buffer_create(size_t bytes, void** dev_ptr, unsigned char handle_out[64]) {
+  if (!dev_ptr || !handle_out || bytes == 0) return EVOATTN_ERR_NULL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void* ptr = nullptr;
+  if (cudaMalloc(&ptr, bytes) != cudaSuccess) return EVOATTN_ERR_CUDA;
+  if (cudaMemset(ptr, 0, bytes) != cudaSuccess) { cudaFree(ptr); return EVOATTN_ERR_CUDA; }
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) { cudaFree(ptr); return EVOATTN_ERR_CUDA; }
+  memcpy(handle_out, &h, 64);
+  *dev_ptr = ptr;
+  return EVOATTN_OK;
+}
+
+int evoattn_peer_buffer_open(const unsigned char handle[64], void** dev_ptr) {
+  if (!handle || !dev_ptr) return EVOATTN_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void* ptr = nullptr;
+  if (cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return EVOATTN_ERR_CUDA;
+  }
+  *dev_ptr = ptr;
+  return EVOATTN_OK;
+}
+
+int evoattn_peer_buffer_close(void* dev_ptr) {
+  return cudaIpcCloseMemHandle(dev_ptr) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+}
+
+int evoattn_peer_buffer_destroy(void* dev_ptr) { return cudaFree(dev_ptr) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA; }
+
+int evoattn_peer_allreduce_f32(const evoattn_peer_allreduce_params* p, void* cuda_stream) {
+  if (!p || !p->bufs || !p->flags) return EVOATTN_ERR_NULL;
+  if (p->world < 1 || p->world > evo::kMaxPeers || p->rank < 0 || p->rank >= p->world) return EVOATTN_ERR_SHAPE;
+  if (p->count == 0) return EVOATTN_OK;
+  evo::PeerArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int q = 0; q < p->world; ++q) {
+    if (!p->bufs[q] || !p->flags[q]) return EVOATTN_ERR_NULL;
+    if (((uintptr_t)p->bufs[q]) & 15) return EVOATTN_ERR_ALIGN;
+    a.buf[q] = p->bufs[q];
+    a.flag[q] = p->flags[q];
+  }
+  a.world = p->world; a.rank = p->rank; a.count = p->count; a.epoch = p->epoch; a.status = p->status;
+  evo::peer_allreduce_kernel<<<evo::kBlocks, evo::kThreads, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+}
+
+}  // extern "C"

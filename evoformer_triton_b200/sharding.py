@@ -3,7 +3,8 @@
 Every (b, h, s) slab is an independent attention problem; only the pair-bias gradient
 couples the N_seq rows (it is their sum, dsevoformer-triton/evoformer.py:458).  So each rank
 runs the unchanged local op on its rows and the job needs exactly one collective: a sum
-all-reduce of d(pair_bias) over NCCL.
+all-reduce of d(pair_bias), over NCCL or, for the GPUs of one node, by this package's own
+peer-memory kernel (:class:`PeerReducer`).
 
 The reference views ``[B, N_seq, N_res, H, D]`` buffers as ``[B, H, N_seq, N_res, D]``
 (evoformer.py:648-650), so "row s" means row s of that *attention view*; slicing axis 1 of
@@ -11,6 +12,7 @@ the label shape would hand out something else.  The helpers below slice in the v
 """
 from __future__ import annotations
 
+import ctypes as C
 from typing import List, Optional, Tuple
 
 import torch
@@ -77,11 +79,109 @@ def replicate_pair_bias(pair_bias: torch.Tensor, group=None) -> torch.Tensor:
     return _SumGradAcrossRanks.apply(pair_bias, group)
 
 
-def sharded_evoformer_attention(attn_fn, Q, K, V, res_mask, pair_bias, group=None):
+class _DeviceBuffer:
+    """A raw device allocation presented to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerReducer:
+    """Sum of the fp32 d(pair_bias) over the GPUs of one node through peer memory.
+
+    The reference runs on one GPU and has no such step (its d_pair_bias is complete after
+    dsevoformer-triton/evoformer.py:458,860).  With the MSA rows sharded, the local partial sums
+    are a few megabytes, for which a library all-reduce is mostly launch and protocol latency.
+    Here every rank maps every other rank's buffer (CUDA IPC over NVLink) and
+    ``evoattn_peer_allreduce_f32`` sums in place with one kernel per rank: rank r adds up slice r
+    over the ranks in a fixed order and stores it into every rank's buffer, between two flag
+    barriers whose waits are bounded.  All ranks end with the same bits.
+
+    Set up once per (group, size); the op's backward writes its local d(pair_bias) straight into
+    ``buffer(numel)`` and calls ``allreduce_``.  Construction is collective over ``group``.
+    """
+
+    def __init__(self, numel: int, device, group=None):
+        from . import _lib
+        self.lib = _lib.load()
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise RuntimeError("PeerReducer serves the (at most 8) GPUs of one node")
+        self.device = torch.device(device)
+        self.numel = int(numel)
+        self.epoch = 0
+        self._own = []
+        self._opened = []
+        with torch.cuda.device(self.device):
+            data_ptr, data_h = self._create(self.numel * 4)
+            flag_ptr, flag_h = self._create(int(self.lib.evoattn_peer_flag_bytes()))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, (data_h, flag_h), group=group)
+            bufs, flags = [], []
+            for q, (dh, fh) in enumerate(handles):
+                if q == self.rank:
+                    bufs.append(data_ptr); flags.append(flag_ptr)
+                else:
+                    bufs.append(self._open(dh)); flags.append(self._open(fh))
+        self._bufs = (C.c_void_p * self.world)(*bufs)
+        self._flags = (C.c_void_p * self.world)(*flags)
+        self._tensor = torch.as_tensor(_DeviceBuffer(data_ptr, self.numel * 4), device=self.device).view(torch.float32)
+        dist.barrier(group=group)  # nobody starts before every rank has mapped every buffer
+
+    def _create(self, nbytes):
+        from . import _lib
+        ptr = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        _lib.check(self.lib.evoattn_peer_buffer_create(C.c_size_t(nbytes), C.byref(ptr), handle), "evoattn_peer_buffer_create")
+        self._own.append(ptr.value)
+        return ptr.value, handle.raw
+
+    def _open(self, handle: bytes):
+        from . import _lib
+        ptr = C.c_void_p()
+        _lib.check(self.lib.evoattn_peer_buffer_open(handle, C.byref(ptr)), "evoattn_peer_buffer_open")
+        self._opened.append(ptr.value)
+        return ptr.value
+
+    def buffer(self, numel: int) -> torch.Tensor:
+        """This rank's part of the exchange buffer (fp32, ``numel`` elements)."""
+        if numel > self.numel:
+            raise ValueError(f"PeerReducer was set up for {self.numel} elements, asked for {numel}")
+        return self._tensor[:numel]
+
+    def allreduce_(self, numel: int) -> None:
+        """In-place sum over the ranks of the first ``numel`` floats of every rank's buffer, on the
+        current stream.  Collective: every rank calls it with the same ``numel``."""
+        from . import _lib, attention
+        self.epoch += 1
+        p = _lib.PeerAllReduceParams()
+        p.world, p.rank = self.world, self.rank
+        p.bufs, p.flags = self._bufs, self._flags
+        p.count, p.epoch = int(numel), self.epoch
+        p.status = attention._status_word(self.device).data_ptr()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.evoattn_peer_allreduce_f32(C.byref(p), C.c_void_p(stream)), "evoattn_peer_allreduce_f32")
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for ptr in self._opened:
+            self.lib.evoattn_peer_buffer_close(C.c_void_p(ptr))
+        dist.barrier(group=self.group)
+        for ptr in self._own:
+            self.lib.evoattn_peer_buffer_destroy(C.c_void_p(ptr))
+        self._opened, self._own = [], []
+
+
+def sharded_evoformer_attention(attn_fn, Q, K, V, res_mask, pair_bias, group=None, peer_reducer=None):
     """Run ``attn_fn`` (``EvoformerAttention.apply`` or a stand-in) on this rank's rows.
 
     Q, K, V, res_mask are already local shards; pair_bias is the full bias.  Forward needs
-    no communication; backward all-reduces d(pair_bias).
+    no communication; backward sums d(pair_bias) over the ranks: with ``peer_reducer`` (a
+    :class:`PeerReducer` of this group) through peer memory, otherwise with an NCCL all-reduce.
     """
     if pair_bias is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
         owner = getattr(attn_fn, "__self__", None)
@@ -90,7 +190,7 @@ def sharded_evoformer_attention(attn_fn, Q, K, V, res_mask, pair_bias, group=Non
             # this package's op: its backward all-reduces the fp32 d(pair_bias) as it leaves the
             # kernel, before the cast to the bias dtype (one collective, no extra conversions, and
             # the local partial sums are never rounded to 16 bits)
-            with attention.pair_bias_grad_summed_over(group):
+            with attention.pair_bias_grad_summed_over(group, peer_reducer):
                 return attn_fn(Q, K, V, res_mask, pair_bias)
         pair_bias = replicate_pair_bias(pair_bias, group)
     return attn_fn(Q, K, V, res_mask, pair_bias)

@@ -146,6 +146,39 @@ int evoattn_bwd(const evoattn_bwd_params* p, void* cuda_stream);
 #define EVOATTN_STATIC_SCRATCH_BYTES (64u << 20)
 int evoattn_bwd_static_scratch(const evoattn_bwd_params* p, void* cuda_stream);
 
+/* ---- Sum over the GPUs of one node through peer memory (for the N_seq-sharded op).
+ *
+ * These have no counterpart in the reference, which runs on one GPU: there d_pair_bias is
+ * complete after the local atomics (evoformer.py:458) and the cast (:860).  When the MSA rows
+ * are sharded over GPUs, every rank holds a partial fp32 d(pair_bias) and the sum over ranks is
+ * the one exchange step of the path.  evoattn_peer_allreduce_f32 does it in place with one kernel
+ * per rank over NVLink (plain peer loads and stores, flag barriers with bounded waits; no
+ * multicast): all ranks call it with the same count and epoch, and afterwards every rank's
+ * buffer holds the same bits.
+ *
+ * Set-up (once, outside the hot path; these are the only functions of the library that allocate):
+ * each rank creates a buffer for the data and one of evoattn_peer_flag_bytes() for the flags,
+ * sends the 64-byte handles to the other ranks (any transport), and opens theirs. */
+typedef struct evoattn_peer_allreduce_params {
+  int32_t world;            /* GPUs taking part, 1..8 */
+  int32_t rank;             /* this GPU's index */
+  float* const* bufs;       /* host array [world]: every rank's data buffer as seen from this rank
+                               (bufs[rank] is this rank's own); 16-byte aligned */
+  uint32_t* const* flags;   /* host array [world]: every rank's flag buffer, zero when created */
+  uint64_t count;           /* floats to sum */
+  uint32_t epoch;           /* 1, 2, 3, ... : one more with every call on these buffers */
+  int32_t* status;          /* optional device word, set when a bounded wait runs out */
+} evoattn_peer_allreduce_params;
+
+size_t evoattn_peer_flag_bytes(void);
+/* cudaMalloc + clear + IPC handle of a buffer other ranks may open. */
+int evoattn_peer_buffer_create(size_t bytes, void** dev_ptr, unsigned char handle_out[64]);
+/* Map another rank's buffer (same node, NVLink / PCIe peer access). */
+int evoattn_peer_buffer_open(const unsigned char handle[64], void** dev_ptr);
+int evoattn_peer_buffer_close(void* dev_ptr);
+int evoattn_peer_buffer_destroy(void* dev_ptr);
+int evoattn_peer_allreduce_f32(const evoattn_peer_allreduce_params* p, void* cuda_stream);
+
 /* EVOATTN_PATH_* of the most recent forward / backward call made by this thread. */
 int evoattn_last_path(void);
 

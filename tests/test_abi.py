@@ -15,7 +15,7 @@ HEADER = os.path.join(ROOT, "include", "evoattn.h")
 def declared_symbols():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(evoattn_[a-z_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(evoattn_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol(built_library):

@@ -1,6 +1,7 @@
-"""Two GPUs: the N_seq-sharded op with its NCCL all-reduce of d(pair_bias) against the same op
-run unsharded on one GPU.  Skipped on a box with fewer than two GPUs (the gloo tests cover the
-partitioning logic on CPU)."""
+"""Two GPUs: the N_seq-sharded op against the same op run unsharded on one GPU, with the sum of
+d(pair_bias) over the ranks done once by an NCCL all-reduce and once by this package's
+peer-memory kernel (plain peer loads and stores over NVLink, NVLS off).  Skipped on a box with
+fewer than two GPUs (the gloo tests cover the partitioning logic on CPU)."""
 import os
 
 import pytest
@@ -9,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, use_peer):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -31,9 +32,23 @@ def _worker(rank, world, port, q):
         loc = {n: sharding.shard_rows(t, rank, world).to(dev) for n, t in full.items()}
         lq, lk, lv = (loc[n].requires_grad_() for n in ("Q", "K", "V"))
         lb = bias.to(dev).requires_grad_()
-        out = sharding.sharded_evoformer_attention(evo.EvoformerAttention.apply, lq, lk, lv,
-                                                   sharding.shard_mask(mask, rank, world).to(dev), lb)
-        out.backward(loc["dO"])
+        reducer = None
+        if use_peer:
+            reducer = sharding.PeerReducer(bias.numel(), dev)
+            # the kernel by itself first: every rank holds (rank + 1) * pattern, twice in a row
+            pattern = torch.arange(1003, device=dev, dtype=torch.float32) * 0.25 - 7.0
+            for rep in range(2):
+                reducer.buffer(1003).copy_(pattern * (rank + 1 + rep))
+                reducer.allreduce_(1003)
+                torch.cuda.synchronize()
+                want = pattern * sum(r + 1 + rep for r in range(world))
+                assert torch.equal(reducer.buffer(1003), want), "peer all-reduce gave a wrong sum"
+        for rep in range(2 if use_peer else 1):  # the exchange buffer is reused by the second call
+            lq.grad = lk.grad = lv.grad = lb.grad = None
+            out = sharding.sharded_evoformer_attention(evo.EvoformerAttention.apply, lq, lk, lv,
+                                                       sharding.shard_mask(mask, rank, world).to(dev), lb,
+                                                       peer_reducer=reducer)
+            out.backward(loc["dO"])
         torch.cuda.synchronize()
         evo.check_device_status()
         parts = [None] * world
@@ -56,18 +71,21 @@ def _worker(rank, world, port, q):
             same_everywhere = all(torch.equal(db[0], d) for d in db[1:])
             rel = float((db[0] - fb.grad.cpu().float()).abs().max() / fb.grad.float().abs().max())
             q.put((errs, same_everywhere, rel))
+        if reducer is not None:
+            reducer.close()
     finally:
         dist.destroy_process_group()
 
 
-def test_two_gpu_sharded_matches_unsharded():
+@pytest.mark.parametrize("use_peer", [False, True], ids=["nccl", "peer_memory"])
+def test_two_gpu_sharded_matches_unsharded(use_peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + (os.getpid() % 400)
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    port = 29500 + (os.getpid() % 400) + (17 if use_peer else 0)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, use_peer)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
