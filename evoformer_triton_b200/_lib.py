@@ -8,10 +8,11 @@ import threading
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libevoattn.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 BF16, FP16, FP32 = 0, 1, 2
 MASK_NONE, MASK_BOOL, MASK_ADD_F32, MASK_ADD_SAME = 0, 1, 2, 3
 FLAG_FORCE_GENERIC = 1
+BIAS_F32, BIAS_SAME = 0, 1
 PATH_NONE, PATH_GENERIC, PATH_TCGEN05 = 0, 1, 2
 
 SYMBOLS = (
@@ -33,7 +34,7 @@ class FwdParams(C.Structure):
         ("q_stride", C.c_int64 * 4), ("k_stride", C.c_int64 * 4),
         ("v_stride", C.c_int64 * 4), ("o_stride", C.c_int64 * 4),
         ("mask", C.c_void_p),
-        ("mask_kind", C.c_int32), ("reserved0", C.c_int32),
+        ("mask_kind", C.c_int32), ("bias_dtype", C.c_int32),
         ("mask_stride", C.c_int64 * 3),
         ("bias", C.c_void_p),
         ("bias_stride", C.c_int64 * 3),

@@ -88,7 +88,10 @@ def _fill_fwd(p: "_lib.FwdParams", q, k, v, o, lse, mask, bias, scale):
     if bias is None:
         p.bias = None
     else:
+        if bias.dtype != torch.float32 and bias.dtype != q.dtype:
+            raise TypeError("pair bias must be float32 or of the q/k/v dtype")
         p.bias = bias.data_ptr()
+        p.bias_dtype = _lib.BIAS_F32 if bias.dtype == torch.float32 else _lib.BIAS_SAME
         bs = bias.stride()
         p.bias_stride = (C.c_int64 * 3)(bs[0], bs[1], bs[2])
     p.status = _status_word(q.device).data_ptr()
@@ -206,7 +209,9 @@ class _EvoformerAttentionBase(torch.autograd.Function):
         bias = None
         if pair_bias is not None:
             bias = pair_bias.reshape(B, H, R, R)  # [B,1,H,R,R] (evoformer.py:652)
-            if bias.dtype != torch.float32:
+            # fp32 (test.py:36-42) and the q/k/v type (memory_benchmark.py:20, speed_benchmark.py:83) are
+            # read by the kernels as they are; anything else is widened once
+            if bias.dtype != torch.float32 and bias.dtype != Q.dtype:
                 bias = bias.float()
             if bias.stride(-1) != 1:
                 bias = bias.contiguous()

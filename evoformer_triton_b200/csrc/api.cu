@@ -44,6 +44,7 @@ int validate_fwd(const evoattn_fwd_params* p) {
   if (p->D > 128) return EVOATTN_ERR_UNSUPPORTED;
   if (p->mask_kind < EVOATTN_MASK_NONE || p->mask_kind > EVOATTN_MASK_ADD_SAME) return EVOATTN_ERR_DTYPE;
   if (p->mask_kind != EVOATTN_MASK_NONE && !p->mask) return EVOATTN_ERR_NULL;
+  if (p->bias_dtype != EVOATTN_BIAS_F32 && p->bias_dtype != EVOATTN_BIAS_SAME) return EVOATTN_ERR_DTYPE;
   if (!(p->scale == p->scale)) return EVOATTN_ERR_SHAPE;  // NaN scale
   return EVOATTN_OK;
 }
@@ -57,8 +58,9 @@ void fill_args(const evoattn_fwd_params* p, evo::Args* a) {
   a->mask = p->mask_kind == EVOATTN_MASK_NONE ? nullptr : p->mask;
   a->mask_kind = p->mask_kind;
   a->smask = evo::Str3{p->mask_stride[0], p->mask_stride[1], p->mask_stride[2]};
-  a->bias = p->bias;
+  a->bias = reinterpret_cast<const float*>(p->bias);
   a->sbias = evo::Str3{p->bias_stride[0], p->bias_stride[1], p->bias_stride[2]};
+  a->bias16 = (p->bias && p->bias_dtype == EVOATTN_BIAS_SAME && p->dtype != EVOATTN_FP32) ? 1 : 0;
   a->status = p->status;
 }
 

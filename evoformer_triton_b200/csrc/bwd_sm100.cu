@@ -98,6 +98,21 @@ __global__ void __launch_bounds__(256) delta_kernel(Args a) {
   a.delta[row] = acc;
 }
 
+// Dense fp32 copy [B,H,R,R] of a pair bias stored in the 16-bit type (these kernels stage the
+// bias as fp32 tiles; the copy lives in the backward's scratch).
+template <class T>
+__global__ void __launch_bounds__(256) widen_bias_kernel(Args a, float* __restrict__ dst) {
+  const long long n = (long long)a.B * a.H * a.R * a.R;
+  for (long long e = (long long)blockIdx.x * 256 + threadIdx.x; e < n; e += (long long)gridDim.x * 256) {
+    const int j = (int)(e % a.R);
+    long long r = e / a.R;
+    const int i = (int)(r % a.R); r /= a.R;
+    const int h = (int)(r % a.H);
+    const int b = (int)(r / a.H);
+    dst[e] = load_bias<T>(a, b, h, i, j);
+  }
+}
+
 // dq = scale * dq_acc, cast to the storage type (dq_acc: contiguous fp32 [B,H,S,R,D]).
 template <class T>
 __global__ void __launch_bounds__(256) dq_convert_kernel(Args a, const float* __restrict__ acc) {
@@ -1018,9 +1033,19 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;
   const size_t delta_bytes = align_up(rows * sizeof(float), 256);
   const size_t dq_bytes = rows * a.D * sizeof(float);
-  if (ws_bytes < delta_bytes + dq_bytes) return EVOATTN_ERR_WORKSPACE;
+  const size_t wide_bytes = (a.bias && a.bias16) ? (size_t)a.B * a.H * a.R * a.R * sizeof(float) : 0;
+  if (ws_bytes < delta_bytes + align_up(dq_bytes, 256) + wide_bytes) return EVOATTN_ERR_WORKSPACE;
   a.delta = reinterpret_cast<float*>(ws);
   float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + delta_bytes);
+  if (wide_bytes) {
+    float* wide = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + delta_bytes + align_up(dq_bytes, 256));
+    const long long n = (long long)a.B * a.H * a.R * a.R;
+    widen_bias_kernel<T><<<(unsigned)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096), 256, 0, st>>>(a, wide);
+    a.bias = wide;
+    a.sbias = Str3{(long long)a.H * a.R * a.R, (long long)a.R * a.R, (long long)a.R};
+    a.bias16 = 0;
+    *launches += 1;
+  }
 
   CUtensorMap tq, tk, tv, tdo, tb;
   if (!make_qkv_map(&tq, a.q, a.sq, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
@@ -1096,7 +1121,8 @@ bool sm100_bwd_supported(int dtype, const Args& a) {
 size_t sm100_bwd_workspace_bytes(int, const Args& a) {
   if (a.D > 16 && a.D <= 32) return sm100_bwdt_workspace_bytes(a);
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;
-  return align_up(rows * sizeof(float), 256) + rows * a.D * sizeof(float);
+  const size_t wide_bytes = (a.bias && a.bias16) ? (size_t)a.B * a.H * a.R * a.R * sizeof(float) : 0;
+  return align_up(rows * sizeof(float), 256) + align_up(rows * a.D * sizeof(float), 256) + wide_bytes;
 }
 
 int launch_sm100_bwd(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,

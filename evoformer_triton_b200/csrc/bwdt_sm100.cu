@@ -51,7 +51,7 @@ struct SmemT {
   static constexpr int kVec = BT * 4;                        // one vector of row statistics
   static constexpr int kStage = 2 * kTile + 2 * kVec;        // Q, dO, -lse*log2e, delta of one step
   static constexpr int kDS = BT * BT * 2;                    // dS^T: two halves of [128 keys][64 queries]
-  static constexpr int kBias = BT * BT * 4;                  // pair-bias tile [128 i][128 j] fp32, unswizzled
+  static constexpr int kBias = BT * BT * 4;                  // pair-bias tile [128 i][128 j], unswizzled (fp32; half of it for a 16-bit bias)
   static constexpr int kOutWarp = 2048;                      // per compute warp: staging of a d_bias chunk or a dQ block
   static constexpr int offKV = 0;                            // [g][K, V], resident for the whole item
   static constexpr int offStage = offKV + 2 * G * kTile;
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(256) dq_store_kernel(Args a, const float* __re
   *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.dq) + off4(a.sdq, b, h, s, i) + d8 * 8) = pk;
 }
 
-template <class T, int DP, bool kHasBias>
+template <class T, int DP, bool kHasBias, bool kBias16>
 __global__ void __launch_bounds__(kThreadsT, 1)
 evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtensorMap tmQ,
                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -195,6 +195,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
   const int NT = (a.R + BT - 1) / BT;
   const int NC = (a.S + G - 1) / G;
   constexpr bool has_bias = kHasBias;
+  constexpr int kBRow = kBias16 ? BT * 2 : BT * 4;  // bytes per row (one query, 128 keys) of the staged bias tile
   const bool flush_dbias = has_bias && a.dbias != nullptr;
   // Persistent CTAs: CTA c owns the items c, c + gridDim.x, ..., SPI steps per item.  A short last
   // row group (S % G != 0) is padded with rows >= S: their tiles and statistics arrive as zeros and
@@ -339,8 +340,8 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       auto load_bias = [&](int t, int h) {
         const StepT d = decode(t * G);
         if (lane == 0) {
-          mbar_expect_tx(b_full + h, L::kBias / 2);
-          tma_load_4d_s(sBias_s + h * (L::kBias / 2), &tmB, (b_full + h).a, d.j0, d.it * BT + h * HT, d.h, d.b);
+          mbar_expect_tx(b_full + h, HT * kBRow);
+          tma_load_4d_s(sBias_s + h * (HT * kBRow), &tmB, (b_full + h).a, d.j0, d.it * BT + h * HT, d.h, d.b);
         }
       };
       const int tiles = my_items * NT;
@@ -418,7 +419,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
     // 32-bit shared-window addresses: every access below stays a shared-memory instruction
     const uint32_t sStage_s = smem_u32(sStage), sDS_s = smem_u32(sDS);
     const uint32_t out_s = smem_u32(sOut) + warp * L::kOutWarp;  // this warp's private staging area
-    const uint32_t brow0 = smem_u32(sBias) + (H * HT + 32 * cb2) * (BT * 4) + jrow * 4;
+    const uint32_t brow0 = smem_u32(sBias) + (H * HT + 32 * cb2) * kBRow + jrow * (kBias16 ? 2 : 4);
     const uint32_t drow = sDS_s + H * (L::kDS / 2) + jrow * 128;
 
     // The residue mask of (b, s, key) in two halves, so that the load can be issued a step before
@@ -531,7 +532,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
         tmem_ld16(cS + 16 * sub, sr);
         tmem_ld16(cP + 16 * sub, dr);
         const uint32_t vnl = vec_s + (H * HT + 32 * cb2 + 16 * sub) * 4, vdl = vnl + BT * 4;
-        const uint32_t brow = brow0 + (16 * sub) * (BT * 4);
+        const uint32_t brow = brow0 + (16 * sub) * kBRow;
         tmem_wait_ld();
         uint32_t pk[8];
         if (!deadstep) {
@@ -543,7 +544,16 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
             const float de[4] = {dl.x, dl.y, dl.z, dl.w};
             if (has_bias) {
 #pragma unroll
-              for (int u = 0; u < 4; ++u) t[u] = fmaf(lds_f32(brow + (4 * c4 + u) * (BT * 4)), kLog2e, t[u]);
+              for (int u = 0; u < 4; ++u) {
+                float bv;
+                if constexpr (kBias16) {
+                  const uint16_t raw = lds_u16(brow + (4 * c4 + u) * kBRow);
+                  bv = to_float<T>(*reinterpret_cast<const T*>(&raw));
+                } else {
+                  bv = lds_f32(brow + (4 * c4 + u) * kBRow);
+                }
+                t[u] = fmaf(bv, kLog2e, t[u]);
+              }
             }
             float p[4], ds[4];
 #pragma unroll
@@ -666,7 +676,9 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   tb = tq;
   tdb = tq;
   if (a.bias) {
-    if (!make_bias_plain_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, HT, BT)) return EVOATTN_ERR_CUDA;
+    const bool ok = a.bias16 ? make_bias16_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, HT, BT, /*swizzle=*/false)
+                             : make_bias_plain_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, HT, BT);
+    if (!ok) return EVOATTN_ERR_CUDA;
     const Str3 dense{(long long)a.H * a.R * a.R, (long long)a.R * a.R, (long long)a.R};
     if (a.dbias && !make_bias_plain_map(&tdb, a.dbias, dense, a.B, a.H, a.R, 16, 32)) return EVOATTN_ERR_CUDA;
   }
@@ -682,7 +694,8 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
     return EVOATTN_ERR_CUDA;
   const long long ctas = items < sms ? items : sms;
-  auto kern = a.bias ? evo_bwdt_kernel<T, DP, true> : evo_bwdt_kernel<T, DP, false>;
+  auto kern = !a.bias ? evo_bwdt_kernel<T, DP, false, false>
+                      : (a.bias16 ? evo_bwdt_kernel<T, DP, true, true> : evo_bwdt_kernel<T, DP, true, false>);
   // setmaxnreg.inc waits until the scheduler's register pool (five warps at the launch-time count)
   // has what it asks for: never launch a build whose pool cannot hold the warps' requests.
   cudaFuncAttributes fa;

@@ -39,8 +39,9 @@ struct Args {
   const void* mask; // [B,S,R]
   int mask_kind;
   Str3 smask;       // (b,s,r)
-  const float* bias;  // [B,H,R,R]
-  Str3 sbias;         // (b,h,i)
+  const float* bias;  // [B,H,R,R]; fp32, or (bias16 != 0) the q/k/v 16-bit type behind this pointer
+  Str3 sbias;         // (b,h,i), in elements of the bias type
+  int bias16;
   // backward only
   const void* d_o;
   void* dq;
@@ -108,6 +109,18 @@ __device__ __forceinline__ float mask_value(const Args& a, int b, int s, int j) 
   if (MIN_MODE) return reinterpret_cast<const unsigned char*>(a.mask)[mi] ? FLT_MAX : -FLT_MAX;
   if (a.mask_kind == EVOATTN_MASK_ADD_F32) return reinterpret_cast<const float*>(a.mask)[mi];
   return to_float<T>(reinterpret_cast<const T*>(a.mask)[mi]);
+}
+
+// Pair-bias element (b, h, i, j) in either storage type.
+template <class T>
+__device__ __forceinline__ float load_bias(const Args& a, int b, int h, int i, int j) {
+  const long long idx = (long long)b * a.sbias.a + (long long)h * a.sbias.b + (long long)i * a.sbias.c + j;
+  if (a.bias16) return to_float<T>(reinterpret_cast<const T*>(a.bias)[idx]);
+  return a.bias[idx];
+}
+template <>
+__device__ __forceinline__ float load_bias<float>(const Args& a, int b, int h, int i, int j) {
+  return a.bias[(long long)b * a.sbias.a + (long long)h * a.sbias.b + (long long)i * a.sbias.c + j];
 }
 
 __device__ __forceinline__ float warp_max(float v) {

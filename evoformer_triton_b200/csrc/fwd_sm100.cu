@@ -78,7 +78,7 @@ __device__ __forceinline__ Item decode_item(int idx, int NSP, int NQT, int H) {
   return it;
 }
 
-template <class T, int DP, int MASKMODE>
+template <class T, int DP, int MASKMODE, bool BIAS16>
 __global__ void __launch_bounds__(kThreads, 1)
 evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CUtensorMap tmQ,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -180,10 +180,15 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
           if (has_bias) {
             const int bs = gt % BST;
             mbar_wait(b_empty(bs), ((gt / BST) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
-            mbar_expect_tx(b_full(bs), C::kBias);
             uint8_t* dst = smem + C::offB + bs * C::kBias;
-            tma_load_4d(dst, &tmB, b_full(bs), t * BN, it.qt * BM, it.h, it.b);
-            tma_load_4d(dst + C::kBias / 2, &tmB, b_full(bs), t * BN + 32, it.qt * BM, it.h, it.b);
+            if constexpr (BIAS16) {  // one box of 128 rows x 64 16-bit values (rows of 128 bytes)
+              mbar_expect_tx(b_full(bs), C::kBias / 2);
+              tma_load_4d(dst, &tmB, b_full(bs), t * BN, it.qt * BM, it.h, it.b);
+            } else {                 // two boxes of 128 rows x 32 floats
+              mbar_expect_tx(b_full(bs), C::kBias);
+              tma_load_4d(dst, &tmB, b_full(bs), t * BN, it.qt * BM, it.h, it.b);
+              tma_load_4d(dst + C::kBias / 2, &tmB, b_full(bs), t * BN + 32, it.qt * BM, it.h, it.b);
+            }
           }
           for (int w = 0; w < 2; ++w) {
             mbar_wait(v_empty(w, st), par, abort_flag, a.status, DEV_TIMEOUT_SYNC);
@@ -335,12 +340,21 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
 #pragma unroll
           for (int g8 = 0; g8 < BN / 8; ++g8) {
             const int c = g8 >> 2, q4 = (g8 & 3) * 2;
-            float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+            float bvv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (has_bias) {
-              b0 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + ((q4 ^ (row & 7)) << 4));
-              b1 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + (((q4 + 1) ^ (row & 7)) << 4));
+              if constexpr (BIAS16) {
+                // eight 16-bit values of my row (rows of 128 bytes, 128-byte swizzle), widened here
+                const uint4 w = *reinterpret_cast<const uint4*>(bstage + ((g8 ^ (row & 7)) << 4));
+                const T* hv = reinterpret_cast<const T*>(&w);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) bvv[u] = to_float<T>(hv[u]);
+              } else {
+                const float4 b0 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + ((q4 ^ (row & 7)) << 4));
+                const float4 b1 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + (((q4 + 1) ^ (row & 7)) << 4));
+                bvv[0] = b0.x; bvv[1] = b0.y; bvv[2] = b0.z; bvv[3] = b0.w;
+                bvv[4] = b1.x; bvv[5] = b1.y; bvv[6] = b1.z; bvv[7] = b1.w;
+              }
             }
-            const float bvv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
             float v[8];
 #pragma unroll
             for (int u = 0; u < 8; u += 2) {  // x = scale*S + bias, two elements per instruction
@@ -530,7 +544,9 @@ int launch_t(const Args& a, cudaStream_t st, int* launches) {
   if (!make_qkv_map(&tk, a.k, a.sk, a.B, a.H, a.S, a.R, a.D, DP, BN)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tv, a.v, a.sv, a.B, a.H, a.S, a.R, a.D, DP, BN)) return EVOATTN_ERR_CUDA;
   if (a.bias) {
-    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BM, 32)) return EVOATTN_ERR_CUDA;
+    const bool ok = a.bias16 ? make_bias16_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BM, BN)
+                             : make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BM, 32);
+    if (!ok) return EVOATTN_ERR_CUDA;
   } else {
     tb = tq;
   }
@@ -541,7 +557,8 @@ int launch_t(const Args& a, cudaStream_t st, int* launches) {
   const long long items = (long long)a.B * a.H * ((a.R + BM - 1) / BM) * ((a.S + 1) / 2);
   const int grid = (int)(items < g_num_sms ? items : g_num_sms);
   const bool add = a.mask_kind == EVOATTN_MASK_ADD_F32 || a.mask_kind == EVOATTN_MASK_ADD_SAME;
-  auto kern = add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD> : evo_fwd_sm100_kernel<T, DP, MASK_MIN>;
+  auto kern = a.bias16 ? (add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD, true> : evo_fwd_sm100_kernel<T, DP, MASK_MIN, true>)
+                       : (add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD, false> : evo_fwd_sm100_kernel<T, DP, MASK_MIN, false>);
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return EVOATTN_ERR_CUDA;
   kern<<<grid, kThreads, smem, st>>>(a, (int)items, tq, tk, tv, tb);
@@ -563,9 +580,10 @@ bool sm100_fwd_supported(int dtype, const Args& a) {
   if (a.D % 8 != 0 || a.D > 64) return false;
   if (a.R > 2048) return false;  // two mask rows are staged in shared memory
   if (a.bias) {
+    const int es = a.bias16 ? 2 : 4;
     if ((reinterpret_cast<uintptr_t>(a.bias) & 15) != 0) return false;
-    if ((a.sbias.a * 4) % 16 || (a.sbias.b * 4) % 16 || (a.sbias.c * 4) % 16) return false;
-    if (a.R % 4 != 0) return false;  // rows of the bias tensor map are whole 16-byte pieces
+    if ((a.sbias.a * es) % 16 || (a.sbias.b * es) % 16 || (a.sbias.c * es) % 16) return false;
+    if ((a.R * es) % 16 != 0) return false;  // rows of the bias tensor map are whole 16-byte pieces
   }
   if ((long long)a.B * a.H * a.S * ((a.R + BM - 1) / BM) > 2147483647LL) return false;
   return true;

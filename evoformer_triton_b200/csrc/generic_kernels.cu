@@ -45,7 +45,7 @@ __device__ __forceinline__ void stage_rows(float* dst, int DP, const T* base, co
 template <class T>
 __device__ __forceinline__ float score(const Args& a, int b, int h, int s, int i, int j, float dot, bool& replaced) {
   float x = dot * a.scale;
-  if (a.bias) x += a.bias[(long long)b * a.sbias.a + (long long)h * a.sbias.b + (long long)i * a.sbias.c + j];
+  if (a.bias) x += load_bias<T>(a, b, h, i, j);
   replaced = false;
   if (a.mask_kind != EVOATTN_MASK_NONE)
     x = apply_mask<T>(x, a.mask, a.mask_kind, (long long)b * a.smask.a + (long long)s * a.smask.b + (long long)j * a.smask.c,

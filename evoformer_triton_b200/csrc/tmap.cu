@@ -107,6 +107,26 @@ bool make_bias_plain_map(CUtensorMap* out, const float* base, const Str3& st, in
   return r == CUDA_SUCCESS;
 }
 
+bool make_bias16_map(CUtensorMap* out, const void* base, const Str3& st, int B, int H, int R, int box_i, int box_j,
+                     bool swizzle) {
+  std::call_once(g_once, resolve);
+  if (!g_encode) return false;
+  const uint64_t row = static_cast<uint64_t>(R) * 2;
+  cuuint64_t dims[4] = {(cuuint64_t)R, (cuuint64_t)R, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {fix_stride(st.c, 2, row, R), fix_stride(st.b, 2, row, H), fix_stride(st.a, 2, row, B)};
+  cuuint32_t box[4] = {(cuuint32_t)box_j, (cuuint32_t)box_i, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const int row_bytes = box_j * 2;
+  CUtensorMapSwizzle swz = !swizzle ? CU_TENSOR_MAP_SWIZZLE_NONE
+                           : row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                           : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                             : CU_TENSOR_MAP_SWIZZLE_32B;
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 bool make_stats_map(CUtensorMap* out, const float* base, int BH, int S, int R, int box_r) {
   std::call_once(g_once, resolve);
   if (!g_encode) return false;

@@ -30,6 +30,12 @@ bool make_rows_f32_plain_map(CUtensorMap* out, const float* base, int D, int R, 
 bool make_bias_plain_map(CUtensorMap* out, const float* base, const Str3& stride_elems, int B, int H, int R, int box_i,
                          int box_j);
 
+// 16-bit [B,H,R,R] pair bias as a 4-D map (R_j, R_i, H, B), box (box_j, box_i, 1, 1): rows of
+// box_j*2 bytes, swizzled with the matching pattern when `swizzle` is set (box_j*2 <= 128), else
+// back to back.
+bool make_bias16_map(CUtensorMap* out, const void* base, const Str3& stride_elems, int B, int H, int R, int box_i,
+                     int box_j, bool swizzle = true);
+
 // Contiguous fp32 per-row statistics [B*H, S, R] as a 3-D map (R, S, B*H) with box (box_r, 1, 1);
 // rows beyond R and MSA rows beyond S read as zero.
 bool make_stats_map(CUtensorMap* out, const float* base, int BH, int S, int R, int box_r);

@@ -114,17 +114,38 @@ class PeerReducer:
         self.epoch = 0
         self._own = []
         self._opened = []
+        err = None
+        bufs, flags = [], []
         with torch.cuda.device(self.device):
-            data_ptr, data_h = self._create(self.numel * 4)
-            flag_ptr, flag_h = self._create(int(self.lib.evoattn_peer_flag_bytes()))
+            try:
+                data_ptr, data_h = self._create(self.numel * 4)
+                flag_ptr, flag_h = self._create(int(self.lib.evoattn_peer_flag_bytes()))
+            except RuntimeError as e:
+                err, data_ptr, flag_ptr, data_h, flag_h = e, 0, 0, None, None
             handles = [None] * self.world
             dist.all_gather_object(handles, (data_h, flag_h), group=group)
-            bufs, flags = [], []
-            for q, (dh, fh) in enumerate(handles):
-                if q == self.rank:
-                    bufs.append(data_ptr); flags.append(flag_ptr)
-                else:
-                    bufs.append(self._open(dh)); flags.append(self._open(fh))
+            if all(h[0] is not None for h in handles):
+                try:
+                    for q, (dh, fh) in enumerate(handles):
+                        if q == self.rank:
+                            bufs.append(data_ptr); flags.append(flag_ptr)
+                        else:
+                            bufs.append(self._open(dh)); flags.append(self._open(fh))
+                except RuntimeError as e:
+                    err = e
+            elif err is None:
+                err = RuntimeError("another rank could not create its exchange buffer")
+        # every rank learns whether all of them succeeded, so that all take the same path
+        ok = torch.tensor([0.0 if err is not None else 1.0], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if ok.item() == 0:
+            for ptr in self._opened:
+                self.lib.evoattn_peer_buffer_close(C.c_void_p(ptr))
+            dist.barrier(group=group)
+            for ptr in self._own:
+                self.lib.evoattn_peer_buffer_destroy(C.c_void_p(ptr))
+            self._opened, self._own = [], []
+            raise RuntimeError(f"peer-memory exchange buffers could not be set up on every rank: {err}")
         self._bufs = (C.c_void_p * self.world)(*bufs)
         self._flags = (C.c_void_p * self.world)(*flags)
         self._tensor = torch.as_tensor(_DeviceBuffer(data_ptr, self.numel * 4), device=self.device).view(torch.float32)

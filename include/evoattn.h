@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define EVOATTN_ABI_VERSION 1
+#define EVOATTN_ABI_VERSION 2
 
 /* status codes (0 = success). */
 enum {
@@ -50,6 +50,14 @@ enum {
   EVOATTN_MASK_BOOL = 1,
   EVOATTN_MASK_ADD_F32 = 2,
   EVOATTN_MASK_ADD_SAME = 3 /* additive, stored in the q/k/v dtype */
+};
+
+/* Storage type of the pair bias.  The reference's callers pass it in fp32 (test.py:36-42) or in
+ * the 16-bit type of q/k/v (memory_benchmark.py:20, speed_benchmark.py:83); the kernels read
+ * either as it is and widen in registers. */
+enum {
+  EVOATTN_BIAS_F32 = 0,
+  EVOATTN_BIAS_SAME = 1 /* stored in the q/k/v dtype (bf16 or fp16) */
 };
 
 /* flags */
@@ -77,9 +85,9 @@ typedef struct evoattn_fwd_params {
   int64_t o_stride[4];
   const void* mask;       /* [B,S,R] or null */
   int32_t mask_kind;
-  int32_t reserved0;
+  int32_t bias_dtype;     /* EVOATTN_BIAS_F32 or EVOATTN_BIAS_SAME */
   int64_t mask_stride[3]; /* element strides of (b,s,r) */
-  const float* bias;      /* pair bias [B,H,R,R] fp32 or null; last axis contiguous */
+  const void* bias;       /* pair bias [B,H,R,R] (type: bias_dtype) or null; last axis contiguous */
   int64_t bias_stride[3]; /* element strides of (b,h,i) */
   int32_t* status;        /* optional device word; a kernel that gives up a bounded wait
                              writes a non-zero code here instead of hanging or trapping */

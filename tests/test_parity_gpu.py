@@ -326,6 +326,25 @@ def test_padded_bias_rows_with_odd_n_res():
         assert oc.rel_err(g, e) < 1e-2, name
 
 
+@pytest.mark.parametrize("cfg", [
+    (1, 5, 200, 2, 32, torch.bfloat16), (1, 4, 384, 2, 32, torch.float16), (2, 3, 256, 2, 64, torch.bfloat16),
+    (1, 6, 136, 4, 8, torch.float16), (1, 3, 100, 2, 32, torch.bfloat16)],
+    ids=lambda c: "B%dS%dR%dH%dD%d-%s" % (c[0], c[1], c[2], c[3], c[4], str(c[5]).split(".")[-1]))
+def test_pair_bias_in_the_storage_type(cfg):
+    """The pair bias in the 16-bit type of q/k/v, as the reference's benchmark scripts pass it
+    (memory_benchmark.py:20, speed_benchmark.py:83): read by the kernels without a widened copy;
+    the oracle gets the same 16-bit bias; d(pair_bias) comes back in that type."""
+    from evoformer_triton_b200 import attention
+    B, S, R, H, D, dtype = cfg
+    x = rand_inputs(B, S, R, H, D, dtype, seed=R + S)
+    x["pair_bias"] = x["pair_bias"].to(dtype)
+    got, paths = run_op(x)
+    if R % 8 == 0:
+        assert paths == (_lib().PATH_TCGEN05, _lib().PATH_TCGEN05)
+    assert got[4].dtype == dtype
+    check(got, x, label=f"16-bit bias {cfg} ")
+
+
 def test_bias_without_gradient_skips_dbias():
     """A pair bias that does not require a gradient (speed_benchmark.py:68): same O, dQ, dK, dV,
     and no d(pair_bias) is computed."""
