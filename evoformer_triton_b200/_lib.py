@@ -20,6 +20,7 @@ SYMBOLS = (
     "evoattn_bwd", "evoattn_bwd_static_scratch", "evoattn_last_path", "evoattn_last_launch_count",
     "evoattn_peer_flag_bytes", "evoattn_peer_buffer_create", "evoattn_peer_buffer_open",
     "evoattn_peer_buffer_close", "evoattn_peer_buffer_destroy", "evoattn_peer_allreduce_f32",
+    "evoattn_bias_to_heads_first", "evoattn_dbias_to_heads_last",
 )
 STATIC_SCRATCH_BYTES = 64 << 20
 
@@ -39,6 +40,8 @@ class FwdParams(C.Structure):
         ("bias", C.c_void_p),
         ("bias_stride", C.c_int64 * 3),
         ("status", C.c_void_p),
+        ("gate", C.c_void_p),
+        ("gate_stride", C.c_int64 * 4),
     ]
 
 
@@ -50,6 +53,9 @@ class BwdParams(C.Structure):
         ("dk_stride", C.c_int64 * 4), ("dv_stride", C.c_int64 * 4),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
+        ("dgate", C.c_void_p),
+        ("dgate_stride", C.c_int64 * 4),
+        ("dmask", C.c_void_p),
     ]
 
 
@@ -101,6 +107,10 @@ def load() -> C.CDLL:
         lib.evoattn_peer_buffer_close.argtypes = [C.c_void_p]
         lib.evoattn_peer_buffer_destroy.restype = C.c_int
         lib.evoattn_peer_buffer_destroy.argtypes = [C.c_void_p]
+        for name in ("evoattn_bias_to_heads_first", "evoattn_dbias_to_heads_last"):
+            fn = getattr(lib, name)
+            fn.restype = C.c_int
+            fn.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         lib.evoattn_peer_allreduce_f32.restype = C.c_int
         lib.evoattn_peer_allreduce_f32.argtypes = [C.POINTER(PeerAllReduceParams), C.c_void_p]
         if lib.evoattn_abi_version() != ABI_VERSION:

@@ -63,7 +63,7 @@ def _require_cuda(t: torch.Tensor):
         raise RuntimeError("EvoformerAttention runs on CUDA tensors only; there is no CPU fallback")
 
 
-def _fill_fwd(p: "_lib.FwdParams", q, k, v, o, lse, mask, bias, scale):
+def _fill_fwd(p: "_lib.FwdParams", q, k, v, o, lse, mask, bias, scale, gate=None):
     B, H, S, R, D = q.shape
     p.dtype = _DTYPES[q.dtype]
     p.B, p.H, p.S, p.R, p.D = B, H, S, R, D
@@ -95,6 +95,11 @@ def _fill_fwd(p: "_lib.FwdParams", q, k, v, o, lse, mask, bias, scale):
         bs = bias.stride()
         p.bias_stride = (C.c_int64 * 3)(bs[0], bs[1], bs[2])
     p.status = _status_word(q.device).data_ptr()
+    if gate is None:
+        p.gate = None
+    else:
+        p.gate = gate.data_ptr()
+        p.gate_stride = _strides4(gate)
 
 
 def _view_dims(x: torch.Tensor, layout: str) -> torch.Tensor:
@@ -118,14 +123,15 @@ def _prep_operand(x: torch.Tensor) -> torch.Tensor:
     return x
 
 
-def attention_forward(q, k, v, mask, bias, scale):
-    """Raw forward on attention-view tensors.  Returns (o, lse)."""
+def attention_forward(q, k, v, mask, bias, scale, gate=None):
+    """Raw forward on attention-view tensors.  Returns (o, lse); with ``gate`` (attention view,
+    same dtype) ``o`` is ``sigmoid(gate) * attention``, multiplied in the kernel's epilogue."""
     lib = _lib.load()
     B, H, S, R, D = q.shape
     o = torch.empty((B, H, S, R, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, H, S, R), dtype=torch.float32, device=q.device)
     p = _lib.FwdParams()
-    _fill_fwd(p, q, k, v, o, lse, mask, bias, scale)
+    _fill_fwd(p, q, k, v, o, lse, mask, bias, scale, gate)
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
         _lib.check(lib.evoattn_fwd(C.byref(p), C.c_void_p(stream)), "evoattn_fwd")
@@ -134,8 +140,11 @@ def attention_forward(q, k, v, mask, bias, scale):
     return o, lse
 
 
-def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True, dbias_out=None):
-    """Raw backward on attention-view tensors.  Returns (dq, dk, dv, dbias fp32 or None).
+def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True, dbias_out=None, gate=None,
+                       want_dmask=False):
+    """Raw backward on attention-view tensors.  Returns (dq, dk, dv, dbias fp32 or None), plus
+    ``dgate`` when ``gate`` is given (``o`` and ``d_o`` are then the gated output and its
+    gradient) and the fp32 ``[B,S,R]`` gradient of an additive mask when ``want_dmask``.
     ``want_dbias=False`` skips d(pair_bias) (its reductions are the backward's largest stream
     of writes; speed_benchmark.py:68 builds the bias without ``requires_grad``)."""
     lib = _lib.load()
@@ -149,7 +158,14 @@ def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True,
         dbias = dbias_out.view(B, H, R, R) if dbias_out is not None else \
             torch.empty((B, H, R, R), dtype=torch.float32, device=q.device)
     p = _lib.BwdParams()
-    _fill_fwd(p.fwd, q, k, v, o, lse, mask, bias, scale)
+    _fill_fwd(p.fwd, q, k, v, o, lse, mask, bias, scale, gate)
+    dgate = dmask = None
+    if gate is not None:
+        dgate = torch.empty((B, H, S, R, D), dtype=q.dtype, device=q.device)
+        p.dgate, p.dgate_stride = dgate.data_ptr(), _strides4(dgate)
+    if want_dmask:
+        dmask = torch.empty((B, S, R), dtype=torch.float32, device=q.device)
+        p.dmask = dmask.data_ptr()
     p.d_o, p.dq, p.dk, p.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     p.dbias = None if dbias is None else dbias.data_ptr()
     p.do_stride, p.dq_stride, p.dk_stride, p.dv_stride = _strides4(d_o), _strides4(dq), _strides4(dk), _strides4(dv)
@@ -161,7 +177,36 @@ def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True,
         _lib.check(lib.evoattn_bwd(C.byref(p), C.c_void_p(stream)), "evoattn_bwd")
     launches["bwd"] = lib.evoattn_last_launch_count()
     last_path["bwd"] = lib.evoattn_last_path()
-    return dq, dk, dv, dbias
+    if gate is None and not want_dmask:
+        return dq, dk, dv, dbias
+    return dq, dk, dv, dbias, dgate, dmask
+
+
+def bias_to_heads_first(bias_brrh: torch.Tensor) -> torch.Tensor:
+    """``[B, R, R, H]`` (as a linear layer emits a pair bias) -> ``[B, H, R, R]``, same dtype, one
+    device pass (the reference's layout, evoformer.py:638,652, makes its caller permute and copy)."""
+    lib = _lib.load()
+    B, R, R2, H = bias_brrh.shape
+    src = bias_brrh.contiguous()
+    dst = torch.empty((B, H, R, R), dtype=src.dtype, device=src.device)
+    stream = torch.cuda.current_stream(src.device).cuda_stream
+    with torch.cuda.device(src.device):
+        _lib.check(lib.evoattn_bias_to_heads_first(src.data_ptr(), dst.data_ptr(), _DTYPES[src.dtype], B, H, R,
+                                                   C.c_void_p(stream)), "evoattn_bias_to_heads_first")
+    return dst
+
+
+def dbias_to_heads_last(dbias_bhrr: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """fp32 ``[B, H, R, R]`` gradient -> ``[B, R, R, H]`` in ``dtype``: the layout change and the one
+    cast of the gradient in a single device pass."""
+    lib = _lib.load()
+    B, H, R, _ = dbias_bhrr.shape
+    dst = torch.empty((B, R, R, H), dtype=dtype, device=dbias_bhrr.device)
+    stream = torch.cuda.current_stream(dst.device).cuda_stream
+    with torch.cuda.device(dst.device):
+        _lib.check(lib.evoattn_dbias_to_heads_last(dbias_bhrr.data_ptr(), dst.data_ptr(), _DTYPES[dtype], B, H, R,
+                                                   C.c_void_p(stream)), "evoattn_dbias_to_heads_last")
+    return dst
 
 
 _pending = threading.local()
@@ -184,12 +229,15 @@ def pair_bias_grad_summed_over(group, peer_reducer=None):
 
 
 class _EvoformerAttentionBase(torch.autograd.Function):
-    """Shared implementation; ``layout`` is fixed by the two public subclasses."""
+    """Shared implementation; ``layout`` (how heads are found in Q/K/V) and ``bias_layout``
+    (``"b1hrr"``: the reference's ``[B, 1, H, R, R]``; ``"brrh"``: ``[B, R, R, H]`` as a linear
+    layer emits it) are fixed by the public subclasses."""
 
     layout = "reinterpret"
+    bias_layout = "b1hrr"
 
     @classmethod
-    def _forward(cls, ctx, Q, K, V, res_mask, pair_bias):
+    def _forward(cls, ctx, Q, K, V, res_mask, pair_bias, gate=None):
         for t in (Q, K, V):
             _require_cuda(t)
         if not (Q.shape[-1] == K.shape[-1] == V.shape[-1]):
@@ -201,6 +249,11 @@ class _EvoformerAttentionBase(torch.autograd.Function):
         if cls.layout == "reinterpret":
             Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
         q, k, v = (_prep_operand(_view_dims(t, cls.layout)) for t in (Q, K, V))
+        g = None
+        if gate is not None:
+            if gate.shape != Q.shape or gate.dtype != Q.dtype:
+                raise TypeError("gate must have the shape and dtype of Q")
+            g = _prep_operand(_view_dims(gate.contiguous() if cls.layout == "reinterpret" else gate, cls.layout))
         mask = None
         if res_mask is not None:
             mask = res_mask.reshape(B, S, R)  # [B,S,1,1,R] in the reference (evoformer.py:651)
@@ -208,33 +261,42 @@ class _EvoformerAttentionBase(torch.autograd.Function):
                 mask = mask.to(torch.float32)
         bias = None
         if pair_bias is not None:
-            bias = pair_bias.reshape(B, H, R, R)  # [B,1,H,R,R] (evoformer.py:652)
+            if cls.bias_layout == "brrh":
+                bias = bias_to_heads_first(pair_bias if pair_bias.dtype in (torch.float32, Q.dtype) else pair_bias.float())
+            else:
+                bias = pair_bias.reshape(B, H, R, R)  # [B,1,H,R,R] (evoformer.py:652)
             # fp32 (test.py:36-42) and the q/k/v type (memory_benchmark.py:20, speed_benchmark.py:83) are
             # read by the kernels as they are; anything else is widened once
             if bias.dtype != torch.float32 and bias.dtype != Q.dtype:
                 bias = bias.float()
             if bias.stride(-1) != 1:
                 bias = bias.contiguous()
-        o, lse = attention_forward(q, k, v, mask, bias, scale)
-        ctx.save_for_backward(q, k, v, mask, bias, o, lse)  # evoformer.py:729
+        o, lse = attention_forward(q, k, v, mask, bias, scale, g)
+        ctx.save_for_backward(q, k, v, mask, bias, o, lse, g)  # evoformer.py:729
         ctx.softmax_scale = scale
         ctx.bias_meta = None if pair_bias is None else (pair_bias.dtype, tuple(pair_bias.shape))
+        ctx.mask_meta = None if res_mask is None else (res_mask.dtype, tuple(res_mask.shape))
         ctx.reduce_group = getattr(_pending, "group", None)
         return _unview(o, cls.layout)
 
     @classmethod
     def _backward(cls, ctx, dO):
-        q, k, v, mask, bias, o, lse = ctx.saved_tensors
+        q, k, v, mask, bias, o, lse, g = ctx.saved_tensors
         if cls.layout == "reinterpret":
             dO = dO.contiguous()  # the reference asserts contiguity instead (evoformer.py:747)
         d_o = _prep_operand(_view_dims(dO, cls.layout))
         if d_o.dtype != q.dtype:
             d_o = d_o.to(q.dtype)
         want_dbias = bias is not None and ctx.needs_input_grad[4]
+        # an additive mask that asks for a gradient gets one (DS4Sci returns gradients for both
+        # biases; the reference returns None, evoformer.py:862)
+        want_dmask = mask is not None and mask.is_floating_point() and ctx.needs_input_grad[3]
         reducer = ctx.reduce_group[1] if (ctx.reduce_group is not None and want_dbias) else None
         dbias_out = reducer.buffer(bias.numel()) if reducer is not None else None
-        dq, dk, dv, dbias = attention_backward(q, k, v, o, lse, mask, bias, ctx.softmax_scale, d_o,
-                                               want_dbias=want_dbias, dbias_out=dbias_out)
+        res = attention_backward(q, k, v, o, lse, mask, bias, ctx.softmax_scale, d_o, want_dbias=want_dbias,
+                                 dbias_out=dbias_out, gate=g, want_dmask=want_dmask)
+        dq, dk, dv, dbias = res[:4]
+        dgate, dmask = (res[4], res[5]) if len(res) > 4 else (None, None)
         d_pair_bias = None
         if dbias is not None:
             dtype, shape = ctx.bias_meta
@@ -244,10 +306,23 @@ class _EvoformerAttentionBase(torch.autograd.Function):
                 import torch.distributed as dist
                 dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=ctx.reduce_group[0])
             # the sum over N_seq stays in fp32 until this single cast (evoformer.py:860 casts to dO's dtype)
-            d_pair_bias = dbias.reshape(shape).to(dtype)
-            if reducer is not None and d_pair_bias.data_ptr() == dbias.data_ptr():
-                d_pair_bias = d_pair_bias.clone()  # the exchange buffer is reused by the next call
-        return _unview(dq, cls.layout), _unview(dk, cls.layout), _unview(dv, cls.layout), None, d_pair_bias
+            if cls.bias_layout == "brrh":
+                d_pair_bias = dbias_to_heads_last(dbias, dtype if dtype in _DTYPES else torch.float32).to(dtype)
+            else:
+                d_pair_bias = dbias.reshape(shape).to(dtype)
+                if reducer is not None and d_pair_bias.data_ptr() == dbias.data_ptr():
+                    d_pair_bias = d_pair_bias.clone()  # the exchange buffer is reused by the next call
+        d_mask = None
+        if dmask is not None:
+            if ctx.reduce_group is None:
+                mdtype, mshape = ctx.mask_meta
+                d_mask = dmask.reshape(mshape).to(mdtype)
+            else:
+                raise RuntimeError("a mask gradient is not available in the N_seq-sharded op (the mask rows are sharded)")
+        grads = (_unview(dq, cls.layout), _unview(dk, cls.layout), _unview(dv, cls.layout), d_mask, d_pair_bias)
+        if g is not None:
+            grads = grads + (_unview(dgate, cls.layout),)
+        return grads
 
 
 class EvoformerAttention(_EvoformerAttentionBase):
@@ -287,7 +362,47 @@ class EvoformerAttentionTrueLayout(_EvoformerAttentionBase):
         return EvoformerAttentionTrueLayout._backward(ctx, dO)
 
 
-def evoformer_attention(Q, K, V, biases: Optional[Sequence[Optional[torch.Tensor]]] = None, *, layout="true"):
+class GatedEvoformerAttention(_EvoformerAttentionBase):
+    """``apply(Q, K, V, res_mask, pair_bias, gate)``: the attention of :class:`EvoformerAttention`
+    followed by the sigmoid gate of a gated-attention block, ``sigmoid(gate) * O`` with ``gate`` of
+    the shape of Q, multiplied in the forward kernel's epilogue; backward returns a gradient for the
+    gate as well.  Not in the reference, whose op ends at O."""
+
+    layout = "reinterpret"
+
+    @staticmethod
+    def forward(ctx, Q, K, V, res_mask, pair_bias, gate):
+        return GatedEvoformerAttention._forward(ctx, Q, K, V, res_mask, pair_bias, gate)
+
+    @staticmethod
+    def backward(ctx, dO):
+        return GatedEvoformerAttention._backward(ctx, dO)
+
+
+def _variant(layout: str, bias_layout: str, gated: bool):
+    """The autograd.Function for a combination of head layout, bias layout and gating."""
+    key = (layout, bias_layout, gated)
+    fn = _VARIANTS.get(key)
+    if fn is None:
+        def forward(ctx, Q, K, V, res_mask=None, pair_bias=None, gate=None):
+            return fn._forward(ctx, Q, K, V, res_mask, pair_bias, gate)
+
+        def backward(ctx, dO):
+            grads = fn._backward(ctx, dO)
+            return grads if len(grads) == 6 else grads + (None,)
+
+        fn = type(f"EvoformerAttention_{layout}_{bias_layout}{'_gated' if gated else ''}", (_EvoformerAttentionBase,),
+                  {"layout": layout, "bias_layout": bias_layout,
+                   "forward": staticmethod(forward), "backward": staticmethod(backward)})
+        _VARIANTS[key] = fn
+    return fn
+
+
+_VARIANTS = {}
+
+
+def evoformer_attention(Q, K, V, biases: Optional[Sequence[Optional[torch.Tensor]]] = None, *, layout="true",
+                        pair_bias_layout="b1hrr", gate=None):
     """List-style call ``attn(Q, K, V, [res_mask_bias, pair_bias])`` of
     ``DS4Sci_EvoformerAttention`` (used at dsevoformer-triton/speed_benchmark.py:24,84).
 
@@ -295,9 +410,13 @@ def evoformer_attention(Q, K, V, biases: Optional[Sequence[Optional[torch.Tensor
     keep-mask when bool); ``biases[1]`` the pair bias ``[B, 1, H, N_res, N_res]``.
     ``layout="true"`` (default) takes heads from axis 3 as DS4Sci does;
     ``layout="reinterpret"`` matches ``EvoformerAttention``.
+    ``pair_bias_layout="brrh"`` takes the pair bias as ``[B, N_res, N_res, H]``, the way a linear
+    layer on the pair representation emits it, and returns its gradient in that layout.
+    ``gate`` (shape of Q) multiplies the output by ``sigmoid(gate)`` inside the kernel.
+    A floating ``res_mask_bias`` that requires a gradient gets one, as in DS4Sci.
     """
     biases = list(biases or [])
     while len(biases) < 2:
         biases.append(None)
-    fn = EvoformerAttentionTrueLayout if layout == "true" else EvoformerAttention
-    return fn.apply(Q, K, V, biases[0], biases[1])
+    fn = _variant("true" if layout == "true" else "reinterpret", pair_bias_layout, gate is not None)
+    return fn.apply(Q, K, V, biases[0], biases[1], gate)

@@ -62,6 +62,8 @@ void fill_args(const evoattn_fwd_params* p, evo::Args* a) {
   a->sbias = evo::Str3{p->bias_stride[0], p->bias_stride[1], p->bias_stride[2]};
   a->bias16 = (p->bias && p->bias_dtype == EVOATTN_BIAS_SAME && p->dtype != EVOATTN_FP32) ? 1 : 0;
   a->status = p->status;
+  a->gate = p->gate;
+  a->sgate = str4(p->gate_stride);
 }
 
 int validate_bwd(const evoattn_bwd_params* p) {
@@ -69,6 +71,7 @@ int validate_bwd(const evoattn_bwd_params* p) {
   int rc = validate_fwd(&p->fwd);
   if (rc) return rc;
   if (!p->d_o || !p->dq || !p->dk || !p->dv) return EVOATTN_ERR_NULL;
+  if (p->fwd.gate && !p->dgate) return EVOATTN_ERR_NULL;
   return EVOATTN_OK;
 }
 
@@ -77,6 +80,7 @@ void fill_bwd_args(const evoattn_bwd_params* p, evo::Args* a) {
   a->d_o = p->d_o; a->dq = p->dq; a->dk = p->dk; a->dv = p->dv;
   a->dbias = p->fwd.bias ? p->dbias : nullptr;
   a->sdo = str4(p->do_stride); a->sdq = str4(p->dq_stride); a->sdk = str4(p->dk_stride); a->sdv = str4(p->dv_stride);
+  a->dmask = p->dmask;
 }
 
 size_t generic_bwd_workspace(const evo::Args& a) {
@@ -88,6 +92,7 @@ bool use_sm100_fwd(const evoattn_fwd_params* p, const evo::Args& a) {
   if (p->dtype == EVOATTN_FP32) return false;
   if (((uintptr_t)p->q | (uintptr_t)p->k | (uintptr_t)p->v | (uintptr_t)p->o) & 15) return false;
   const int es = esize_of(p->dtype);
+  if (p->gate && ((((uintptr_t)p->gate) & 15) || !stride_ok16(p->gate_stride, es))) return false;
   if (!stride_ok16(p->q_stride, es) || !stride_ok16(p->k_stride, es) || !stride_ok16(p->v_stride, es) ||
       !stride_ok16(p->o_stride, es))
     return false;
@@ -96,6 +101,7 @@ bool use_sm100_fwd(const evoattn_fwd_params* p, const evo::Args& a) {
 
 bool use_sm100_bwd(const evoattn_bwd_params* p, const evo::Args& a) {
   if (!use_sm100_fwd(&p->fwd, a)) return false;
+  if (p->dmask) return false;  // the gradient of an additive mask is produced by the CUDA-core kernels
   if (((uintptr_t)p->d_o | (uintptr_t)p->dq | (uintptr_t)p->dk | (uintptr_t)p->dv) & 15) return false;
   const int es = esize_of(p->fwd.dtype);
   if (!stride_ok16(p->do_stride, es) || !stride_ok16(p->dq_stride, es) || !stride_ok16(p->dk_stride, es) ||
@@ -132,6 +138,36 @@ int static_scratch_address(void** out) {
   }
   *out = ptr;
   return EVOATTN_OK;
+}
+
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+// Scratch of a backward call: what the kernel family needs, then (gated output) the effective dO.
+size_t path_scratch_need(const evoattn_bwd_params* p, const evo::Args& a, bool fast) {
+  return align256(fast ? evo::sm100_bwd_workspace_bytes(p->fwd.dtype, a) : generic_bwd_workspace(a));
+}
+size_t bwd_scratch_need(const evoattn_bwd_params* p, const evo::Args& a, bool fast) {
+  return path_scratch_need(p, a, fast) + (p->fwd.gate ? evo::gate_backward_scratch_bytes(p->fwd.dtype, a) : 0);
+}
+
+// The backward with its scratch at `scratch` (caller-provided or the static array).
+int run_bwd(const evoattn_bwd_params* p, evo::Args& a, bool fast, void* scratch, cudaStream_t st) {
+  const size_t path_bytes = path_scratch_need(p, a, fast);
+  a.delta = reinterpret_cast<float*>(scratch);  // every kernel family keeps delta at the start of its scratch
+  if (p->fwd.gate) {
+    const int rc = evo::launch_gate_backward(p->fwd.dtype, &a, reinterpret_cast<unsigned char*>(scratch) + path_bytes, p->dgate,
+                                             str4(p->dgate_stride), st, &g_last_launches);
+    if (rc) return rc;
+  }
+  if (a.dmask &&
+      cudaMemsetAsync(a.dmask, 0, (size_t)a.B * a.S * a.R * sizeof(float), st) != cudaSuccess)
+    return EVOATTN_ERR_CUDA;
+  if (fast) {
+    g_last_path = EVOATTN_PATH_TCGEN05;
+    return evo::launch_sm100_bwd(p->fwd.dtype, a, scratch, path_bytes, st, &g_last_launches);
+  }
+  g_last_path = EVOATTN_PATH_GENERIC;
+  return evo::launch_generic_bwd(p->fwd.dtype, a, st, &g_last_launches) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
 }
 
 }  // namespace
@@ -176,8 +212,7 @@ size_t evoattn_bwd_workspace_bytes(const evoattn_bwd_params* p) {
   if (validate_bwd(p)) return 0;
   evo::Args a;
   fill_bwd_args(p, &a);
-  if (use_sm100_bwd(p, a)) return evo::sm100_bwd_workspace_bytes(p->fwd.dtype, a);
-  return generic_bwd_workspace(a);
+  return bwd_scratch_need(p, a, use_sm100_bwd(p, a));
 }
 
 int evoattn_bwd(const evoattn_bwd_params* p, void* cuda_stream) {
@@ -187,19 +222,12 @@ int evoattn_bwd(const evoattn_bwd_params* p, void* cuda_stream) {
   if (rc) return rc;
   evo::Args a;
   fill_bwd_args(p, &a);
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
   bind_context_once();
   const bool fast = use_sm100_bwd(p, a);
-  const size_t need = fast ? evo::sm100_bwd_workspace_bytes(p->fwd.dtype, a) : generic_bwd_workspace(a);
+  const size_t need = bwd_scratch_need(p, a, fast);
   if (need && (!p->workspace || p->workspace_bytes < need)) return EVOATTN_ERR_WORKSPACE;
   if (need && ((uintptr_t)p->workspace & 255)) return EVOATTN_ERR_ALIGN;
-  if (fast) {
-    g_last_path = EVOATTN_PATH_TCGEN05;
-    return evo::launch_sm100_bwd(p->fwd.dtype, a, p->workspace, p->workspace_bytes, st, &g_last_launches);
-  }
-  g_last_path = EVOATTN_PATH_GENERIC;
-  a.delta = reinterpret_cast<float*>(p->workspace);
-  return evo::launch_generic_bwd(p->fwd.dtype, a, st, &g_last_launches) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+  return run_bwd(p, a, fast, p->workspace, reinterpret_cast<cudaStream_t>(cuda_stream));
 }
 
 int evoattn_bwd_static_scratch(const evoattn_bwd_params* p, void* cuda_stream) {
@@ -209,22 +237,14 @@ int evoattn_bwd_static_scratch(const evoattn_bwd_params* p, void* cuda_stream) {
   if (rc) return rc;
   evo::Args a;
   fill_bwd_args(p, &a);
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
   const bool fast = use_sm100_bwd(p, a);
-  const size_t need = fast ? evo::sm100_bwd_workspace_bytes(p->fwd.dtype, a) : generic_bwd_workspace(a);
-  if (need > EVOATTN_STATIC_SCRATCH_BYTES) return EVOATTN_ERR_WORKSPACE;
+  if (bwd_scratch_need(p, a, fast) > EVOATTN_STATIC_SCRATCH_BYTES) return EVOATTN_ERR_WORKSPACE;
   // Looking the symbol up (done on every call) also makes the device's primary context current
   // on this thread, which the tensor-map encoder needs; nothing here allocates.
   void* scratch = nullptr;
   rc = static_scratch_address(&scratch);
   if (rc) return rc;
-  if (fast) {
-    g_last_path = EVOATTN_PATH_TCGEN05;
-    return evo::launch_sm100_bwd(p->fwd.dtype, a, scratch, EVOATTN_STATIC_SCRATCH_BYTES, st, &g_last_launches);
-  }
-  g_last_path = EVOATTN_PATH_GENERIC;
-  a.delta = reinterpret_cast<float*>(scratch);
-  return evo::launch_generic_bwd(p->fwd.dtype, a, st, &g_last_launches) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+  return run_bwd(p, a, fast, scratch, reinterpret_cast<cudaStream_t>(cuda_stream));
 }
 
 int evoattn_last_path(void) { return g_last_path; }

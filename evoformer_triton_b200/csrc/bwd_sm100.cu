@@ -1067,7 +1067,7 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (a.dbias &&
       cudaMemsetAsync(a.dbias, 0, (size_t)a.B * a.H * a.R * a.R * sizeof(float), st) != cudaSuccess)
     return EVOATTN_ERR_CUDA;
-  delta_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(a);
+  if (!a.delta_ready) delta_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(a);
 
   const int NT = (a.R + BT - 1) / BT;
   const bool add = a.mask_kind == EVOATTN_MASK_ADD_F32 || a.mask_kind == EVOATTN_MASK_ADD_SAME;

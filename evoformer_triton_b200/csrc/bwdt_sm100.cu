@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(256) prep_kernel(Args a, float* __restrict__ n
 #pragma unroll
     for (int u = 0; u < 8; ++u) acc += to_float<T>(op[u]) * to_float<T>(gp[u]);
   }
-  a.delta[row] = acc;
+  if (!a.delta_ready) a.delta[row] = acc;
   const float lse = a.lse[row];
   nl[row] = (lse == -FLT_MAX) ? __int_as_float(0x7f800000) : -lse * kLog2e;
 }

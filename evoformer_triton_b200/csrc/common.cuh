@@ -51,6 +51,11 @@ struct Args {
   float* delta;     // [B,H,S,R] (workspace)
   Str4 sdo, sdq, sdk, sdv;
   int* status;
+  // gated output (optional): forward multiplies O by sigmoid(gate); backward gets dO of the gated output
+  const void* gate;
+  Str4 sgate;
+  int delta_ready;  // backward: delta has been written already (gated path), the kernels must not recompute it
+  float* dmask;     // backward (CUDA-core kernels only): gradient of an additive mask, [B,S,R] fp32
 };
 
 template <class T> __device__ __forceinline__ float to_float(T x);
@@ -122,6 +127,8 @@ template <>
 __device__ __forceinline__ float load_bias<float>(const Args& a, int b, int h, int i, int j) {
   return a.bias[(long long)b * a.sbias.a + (long long)h * a.sbias.b + (long long)i * a.sbias.c + j];
 }
+
+__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.f / (1.f + __expf(-x)); }
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

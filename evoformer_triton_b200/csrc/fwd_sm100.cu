@@ -495,14 +495,24 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
       if (active && i < a.R) {
         const float inv = 1.f / l_run;
         T* orow = reinterpret_cast<T*>(a.o) + off4(a.so, it.b, it.h, s, i);
+        const T* grow = a.gate ? reinterpret_cast<const T*>(a.gate) + off4(a.sgate, it.b, it.h, s, i) : nullptr;
 #pragma unroll
         for (int d8 = 0; d8 < DP / 8; ++d8) {
           if (d8 * 8 < a.D) {
+            float f[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) f[u] = acc[d8 * 8 + u] * inv;
+            if (grow != nullptr) {  // gated output: O * sigmoid(gate), in the epilogue
+              const uint4 gw = *reinterpret_cast<const uint4*>(grow + d8 * 8);
+              const T* gv = reinterpret_cast<const T*>(&gw);
+#pragma unroll
+              for (int u = 0; u < 8; ++u) f[u] *= sigmoidf_fast(to_float<T>(gv[u]));
+            }
             uint4 v4;
-            v4.x = Pack2<T>::pack(acc[d8 * 8 + 0] * inv, acc[d8 * 8 + 1] * inv);
-            v4.y = Pack2<T>::pack(acc[d8 * 8 + 2] * inv, acc[d8 * 8 + 3] * inv);
-            v4.z = Pack2<T>::pack(acc[d8 * 8 + 4] * inv, acc[d8 * 8 + 5] * inv);
-            v4.w = Pack2<T>::pack(acc[d8 * 8 + 6] * inv, acc[d8 * 8 + 7] * inv);
+            v4.x = Pack2<T>::pack(f[0], f[1]);
+            v4.y = Pack2<T>::pack(f[2], f[3]);
+            v4.z = Pack2<T>::pack(f[4], f[5]);
+            v4.w = Pack2<T>::pack(f[6], f[7]);
             *reinterpret_cast<uint4*>(orow + d8 * 8) = v4;
           }
         }

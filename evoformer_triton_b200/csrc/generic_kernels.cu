@@ -107,11 +107,12 @@ __global__ void __launch_bounds__(GW * 32) generic_fwd_kernel(Args a) {
   }
   if (row_ok) {
     T* o = reinterpret_cast<T*>(a.o) + off4(a.so, sl.b, sl.h, sl.s, i);
+    const T* gate = a.gate ? reinterpret_cast<const T*>(a.gate) + off4(a.sgate, sl.b, sl.h, sl.s, i) : nullptr;
     const float inv = 1.f / l;
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const int d = lane + 32 * t;
-      if (d < D) o[d] = from_float<T>(acc[t] * inv);
+      if (d < D) o[d] = from_float<T>(acc[t] * inv * (gate ? sigmoidf_fast(to_float<T>(gate[d])) : 1.f));
     }
     if (lane == 0) a.lse[((long long)blockIdx.x) * a.R + i] = m + logf(l);
   }
@@ -217,6 +218,7 @@ __global__ void __launch_bounds__(GW * 32) generic_dkdv_kernel(Args a) {
     Vw[warp * DP + d] = to_float<T>(v[d]);
   }
   float accK[4] = {0.f, 0.f, 0.f, 0.f}, accV[4] = {0.f, 0.f, 0.f, 0.f};
+  float dmask_acc = 0.f;  // this lane's share of sum_i dS_ij (gradient of an additive mask)
   for (int i0 = 0; i0 < a.R; i0 += GT) {
     __syncthreads();
     stage_rows<T>(Qs, DP, reinterpret_cast<const T*>(a.q), a.sq, sl.b, sl.h, sl.s, i0, a.R, D);
@@ -239,6 +241,7 @@ __global__ void __launch_bounds__(GW * 32) generic_dkdv_kernel(Args a) {
       const float x = score<T>(a, sl.b, sl.h, sl.s, i, jc, dot, rep);
       p = prob_from_lse(x, Ls[lane], a.R);
       ds = rep ? 0.f : p * (dp - Ds[lane]);
+      dmask_acc += ds;
     }
     for (int ii = 0; ii < GT; ++ii) {
       const float pi = __shfl_sync(0xffffffffu, p, ii);
@@ -252,6 +255,10 @@ __global__ void __launch_bounds__(GW * 32) generic_dkdv_kernel(Args a) {
         }
       }
     }
+  }
+  if (a.dmask != nullptr) {  // one addition per (b,h,s,j): the sum over heads
+    const float tot = warp_sum(dmask_acc);
+    if (row_ok && lane == 0) atomicAdd(a.dmask + ((long long)sl.b * a.S + sl.s) * a.R + j, tot);
   }
   if (row_ok) {
     T* ok = reinterpret_cast<T*>(a.dk) + off4(a.sdk, sl.b, sl.h, sl.s, j);
@@ -325,7 +332,7 @@ template <class T>
 static cudaError_t launch_bwd_t(const Args& a, cudaStream_t st, int* launches) {
   const int DP = a.D + 1;
   const long long rows = (long long)a.B * a.H * a.S * a.R;
-  generic_delta_kernel<T><<<(unsigned)((rows + GW - 1) / GW), GW * 32, 0, st>>>(a);
+  if (!a.delta_ready) generic_delta_kernel<T><<<(unsigned)((rows + GW - 1) / GW), GW * 32, 0, st>>>(a);
   dim3 grid(a.B * a.H * a.S, (a.R + GW - 1) / GW);
   generic_dq_kernel<T><<<grid, GW * 32, (size_t)(2 * GT + 2 * GW) * DP * sizeof(float), st>>>(a);
   generic_dkdv_kernel<T><<<grid, GW * 32, ((size_t)(2 * GT + 2 * GW) * DP + 2 * GT) * sizeof(float), st>>>(a);

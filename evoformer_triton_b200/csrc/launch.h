@@ -26,4 +26,9 @@ size_t sm100_bwdt_workspace_bytes(const Args& a);
 int launch_sm100_bwdt(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
                       int* launches);
 
+// Backward half of the gated output (extras.cu): writes delta, the effective dO (into `scratch`) and
+// dgate, and redirects `a` to the effective dO.
+size_t gate_backward_scratch_bytes(int dtype, const Args& a);
+int launch_gate_backward(int dtype, Args* a, void* scratch, void* dgate, const Str4& sdgate, cudaStream_t st, int* launches);
+
 }  // namespace evo

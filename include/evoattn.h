@@ -91,6 +91,11 @@ typedef struct evoattn_fwd_params {
   int64_t bias_stride[3]; /* element strides of (b,h,i) */
   int32_t* status;        /* optional device word; a kernel that gives up a bounded wait
                              writes a non-zero code here instead of hanging or trapping */
+  const void* gate;       /* optional gating logits, attention view, q/k/v dtype: the output becomes
+                             sigmoid(gate) * O, applied in the kernel's epilogue (the step that follows
+                             the attention in a gated-attention block; the reference has no such input).
+                             Null: plain attention, as the reference computes it */
+  int64_t gate_stride[4]; /* element strides of (b,h,s,r) */
 } evoattn_fwd_params;
 
 typedef struct evoattn_bwd_params {
@@ -109,6 +114,13 @@ typedef struct evoattn_bwd_params {
   int64_t dv_stride[4];
   void* workspace;        /* device scratch of at least evoattn_bwd_workspace_bytes() */
   size_t workspace_bytes;
+  void* dgate;            /* out, gradient of fwd.gate (same dtype), required when fwd.gate is set;
+                             d_o is then the gradient of the GATED output and fwd.o the gated output */
+  int64_t dgate_stride[4];
+  float* dmask;           /* optional out, fp32 [B,S,R] contiguous: gradient of an additive mask
+                             (sum of dS over heads and queries; DS4Sci returns a gradient for both
+                             biases, the reference returns None, evoformer.py:862).  Requests with
+                             dmask set are served by the CUDA-core kernels */
 } evoattn_bwd_params;
 
 /* ABI version of the loaded library; compare with EVOATTN_ABI_VERSION. */
@@ -186,6 +198,15 @@ int evoattn_peer_buffer_open(const unsigned char handle[64], void** dev_ptr);
 int evoattn_peer_buffer_close(void* dev_ptr);
 int evoattn_peer_buffer_destroy(void* dev_ptr);
 int evoattn_peer_allreduce_f32(const evoattn_peer_allreduce_params* p, void* cuda_stream);
+
+/* ---- Pair bias in the layout a linear layer emits it, [B, R, R, H] (heads last).
+ *
+ * The reference takes the bias as [B, 1, H, R, R] (evoformer.py:638,652), which makes its caller
+ * permute and copy an R*R*H tensor on every call, and the same for the gradient.  These two
+ * kernels do that conversion on the device in one pass each; the second also casts the fp32
+ * gradient to the bias type on the way.  `dtype` is the element type of the 16/32-bit side. */
+int evoattn_bias_to_heads_first(const void* src_brrh, void* dst_bhrr, int dtype, int B, int H, int R, void* cuda_stream);
+int evoattn_dbias_to_heads_last(const float* src_bhrr, void* dst_brrh, int dtype, int B, int H, int R, void* cuda_stream);
 
 /* EVOATTN_PATH_* of the most recent forward / backward call made by this thread. */
 int evoattn_last_path(void);

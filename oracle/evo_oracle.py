@@ -143,6 +143,47 @@ def attention_fwd_bwd(
             None if bias is None else bias.grad)
 
 
+def extended_attention_fwd_bwd(Q, K, V, res_mask, pair_bias, dO, *, gate=None, pair_bias_layout="b1hrr",
+                               layout: str = "reinterpret", upcast: Optional[torch.dtype] = None):
+    """The naive path with the extensions that lie just outside the reference's op, composed from
+    plain PyTorch and differentiated by autograd: a sigmoid gate on the output
+    (``sigmoid(gate) * O``, the step after the attention in a gated-attention block), a pair bias
+    given as ``[B, N_res, N_res, H]`` (as a linear layer emits it; the reference takes
+    ``[B, 1, H, N_res, N_res]``, evoformer.py:638), and a gradient for an additive mask (which
+    DS4Sci returns and the reference does not, evoformer.py:862).  The reference has none of
+    these, so nothing pins them beyond this composition of the pinned ``attention_kernel_view``.
+
+    Returns ``(O, dQ, dK, dV, d_pair_bias, d_gate, d_mask)`` (None where not applicable);
+    d_pair_bias is in the layout the bias came in.
+    """
+    B, S, R, H, D = Q.shape
+
+    def prep(t, grad=False):
+        if t is None:
+            return None
+        t = t.detach()
+        if upcast is not None and t.is_floating_point():
+            t = t.to(upcast)
+        return t.clone().requires_grad_() if grad else t
+
+    q, k, v = (prep(t, True) for t in (Q, K, V))
+    bias = prep(pair_bias, True)
+    g = prep(gate, True)
+    mask_grad = res_mask is not None and res_mask.is_floating_point()
+    mask = prep(res_mask, mask_grad)
+    b5 = None
+    if bias is not None:
+        b5 = bias.permute(0, 3, 1, 2).reshape(B, H, 1, R, R) if pair_bias_layout == "brrh" else bias.reshape(B, H, 1, R, R)
+    m5 = None if mask is None else mask.reshape(B, 1, S, 1, R)
+    o = attention_kernel_view(kernel_view(q, layout), kernel_view(k, layout), kernel_view(v, layout), m5, b5)
+    o = label_view(o, layout)
+    if g is not None:
+        o = o * torch.sigmoid(g)
+    o.backward(prep(dO).to(o.dtype))
+    return (o.detach(), q.grad, k.grad, v.grad, None if bias is None else bias.grad,
+            None if g is None else g.grad, mask.grad if mask_grad else None)
+
+
 def attention_fwd_bwd_explicit(Q, K, V, res_mask, pair_bias, dO, *, layout="reinterpret"):
     """The same function with the backward written out by hand in fp64.
 
