@@ -1,4 +1,5 @@
-// Evoformer attention backward for sm_100a: one fused kernel recomputes P and produces
+// Evoformer attention backward for sm_100a, head dimensions 33..64 (smaller ones are served by
+// the kernel with transposed score tiles in bwdt_sm100.cu): one fused kernel recomputes P and produces
 // dQ, dK, dV and d(pair_bias) with tcgen05 MMAs (accumulators in TMEM) and TMA-staged tiles.
 //
 // Replaces dsevoformer-triton/evoformer.py:299-326 (_attn_bwd_preprocess), :479-630
@@ -7,9 +8,8 @@
 // computed once, and a CTA sums dS over a group of G MSA rows in registers before it
 // touches memory, so d(pair_bias) sees one reduction per CTA tile.
 //
-// Decomposition: a work item is a 128-key tile j of G consecutive MSA rows s of one (b,h); the
-// DP = 64 kernel runs one CTA per item, the DP <= 32 kernel one persistent CTA per SM that walks
-// the items blockIdx.x, blockIdx.x + gridDim.x, ...  For an item:
+// Decomposition: a work item is a 128-key tile j of G consecutive MSA rows s of one (b,h), one CTA
+// per item.  For an item:
 //   for each 128-query tile i:             (pair-bias tile (i,j) is the same for all s)
 //     for each of the G rows s:
 //       S  = Q_i K_j^T, dP = dO_i V_j^T                      (2 MMAs -> TMEM)
@@ -465,564 +465,6 @@ evo_bwd_sm100_kernel(const Args a, float* __restrict__ dq_acc, const __grid_cons
 }
 
 
-// ---------------------------------------------------------------------------------------
-// Warp-specialised, persistent variant for DP <= 32 (384 threads, one CTA per SM): warps 0-7
-// compute as above, warp 8 is a control warp whose lane 0 issues the Q/dO/K/V loads and every
-// tcgen05.mma, warps 9 and 10 feed the pair bias to compute warpgroup 0 and 1.
-//   * A CTA walks its work items (a 128-key tile of G MSA rows of one (b,h)) as one flat list of
-//     steps; the tiles of a step arrive two steps ahead in a two-deep ring, across item ends too.
-//   * S and dP are issued per compute warpgroup (64 key columns each, own barrier): a warpgroup
-//     hands its columns back as soon as it holds them in registers, half a step before it needs
-//     the next ones, so the step never starts with a wait for the tensor core.
-//   * The pair bias of one block of 32 key columns (two 128x16 fp32 chunks) per warpgroup is all
-//     that fits in shared memory; the next block is requested the moment the current one has
-//     been read into registers and lands while it is being worked on.
-//   * P and dS are double-buffered in shared memory: the dV/dK/dQ MMAs of step n run underneath
-//     step n+1's arithmetic.  (An MMA whose A operand comes from shared memory costs about as
-//     many cycles as its operand bytes / 64: the 24 small MMAs of a step take a third of it.)
-//   * The dQ partial of step n leaves TMEM at the end of step n+1 and is added to the fp32
-//     accumulator in global memory piecewise during step n+2; d_bias tiles are staged in the
-//     P/dS halves the warpgroup writes next and leave through bulk tensor reductions whose
-//     shared-memory reads run underneath the next step's first block of arithmetic; dK/dV of an
-//     item leave TMEM during the first steps of the next item.
-// G = 3 rows per item: S 128 + dP 128 + 3*(dV 32 + dK 32) + dQ 32 = 480 TMEM columns.
-template <int DP>
-struct WsSmem {
-  static constexpr int G = 3;
-  static constexpr int RB = DP * 2;
-  static constexpr int kTile = BT * RB;
-  static constexpr int kPS = BT * BT * 2;
-  static constexpr int kBiasChunk = BT * 64;             // 128 rows x 16 fp32, 64-byte swizzle
-  static constexpr int kStage = 4 * kTile;               // Q, dO, K, V of one step
-  static constexpr int offStage = 0;                      // 2 stages
-  static constexpr int offP = offStage + 2 * kStage;      // 2 buffers
-  static constexpr int offDS = offP + 2 * kPS;            // 2 buffers
-  static constexpr int offB = offDS + 2 * kPS;            // [warpgroup][2] chunk buffers
-  static constexpr int offMask = offB + 4 * kBiasChunk;   // G x 128 floats
-  static constexpr int offBars = offMask + G * BT * 4;
-  static constexpr size_t bytes = offBars + 256 + 1024;
-};
-
-// One step of the flat work list: batch, head, MSA row, query tile, row-group slot, first key.
-struct StepId {
-  int b, h, s, it, g, j0;
-};
-
-template <class T, int DP, int MASKMODE>
-__global__ void __launch_bounds__(384, 1)
-evo_bwd_ws_kernel(const Args a, float* __restrict__ dq_acc, const int n_items, const __grid_constant__ CUtensorMap tmQ,
-                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                  const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmDB) {
-  using L = WsSmem<DP>;
-  constexpr int G = L::G;
-  constexpr int RB = L::RB;
-  constexpr uint32_t SWZ = swizzle_code_for_row_bytes(RB);
-  constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-  constexpr int HALF_D = DP / 2;
-  constexpr int kTmemCols = 512;
-  constexpr int colS = 0, colDP = BT, colDV = 2 * BT, colDK = 2 * BT + G * DP, colDQ = 2 * BT + 2 * G * DP;
-  static_assert(colDQ + DP <= kTmemCols, "TMEM budget");
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sP = smem + L::offP;
-  uint8_t* sDS = smem + L::offDS;
-  uint8_t* sB = smem + L::offB;
-  float* sMask = reinterpret_cast<float*>(smem + L::offMask);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBars);
-  uint64_t* bar_ld = bars + 0;      // [2] tiles of a step landed
-  uint64_t* bar_sdp = bars + 2;     // [2 warpgroups] that warpgroup's 64 key columns of S, dP complete
-  uint64_t* bar_out = bars + 4;     // dV, dK, dQ MMAs of a step complete
-  uint64_t* bar_bfull = bars + 5;   // [2 warpgroups] the pair-bias block (two chunks) of that warpgroup landed
-  uint64_t* bar_bempty = bars + 9;  // [2 warpgroups] ... has been read, one arrival per warp
-  uint64_t* bar_sread = bars + 13;  // [2 warpgroups] that warpgroup has read its S, dP columns (one arrival per warp)
-  uint64_t* bar_cdone = bars + 15;  // the 8 compute warps finished a step (P, dS written; dQ read)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
-  volatile uint32_t* scratch = reinterpret_cast<volatile uint32_t*>(bars + 18);  // written, never read
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int NT = (a.R + BT - 1) / BT;
-  const int NC = (a.S + G - 1) / G;
-  const bool has_bias = a.bias != nullptr;
-  // Persistent CTAs: CTA c owns the items c, c + gridDim.x, ... (an item = one 128-key tile of G
-  // consecutive MSA rows of one (b,h)) and walks them as one flat sequence of steps, SPI per item,
-  // so that the loads and the S/dP MMAs of an item's first steps run underneath the previous
-  // item's last ones.  A short last row group (S % G != 0) is padded with rows >= S: their tiles
-  // arrive as zeros and their lse is huge, so P = dS = 0, and nothing of them is stored.
-  const int SPI = NT * G;
-  const int my_items = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int total_steps = my_items * SPI;
-  auto decode = [&](int N) {
-    StepId d;
-    const int k = N / SPI, n = N - k * SPI;
-    d.it = n / G;
-    d.g = n - d.it * G;
-    int idx = (int)blockIdx.x + k * (int)gridDim.x;
-    const int chunk = idx % NC; idx /= NC;
-    d.j0 = (idx % NT) * BT; idx /= NT;
-    d.h = idx % a.H;
-    d.b = idx / a.H;
-    d.s = chunk * G + d.g;
-    return d;
-  };
-  // residue mask of MSA row s, key j as the float the compute warps combine with a score
-  auto mask_of = [&](int b, int s, int j) -> float {
-    if (s >= a.S) return -FLT_MAX;
-    return mask_value<T, MASKMODE == MASK_MIN ? 1 : 0>(a, b, s, j);
-  };
-  // The same in two halves, so that the load can be issued long before its value is needed:
-  // the raw mask element (0 where there is none to read) ...
-  auto mask_fetch = [&](int b, int s, int j) -> uint32_t {
-    if (s >= a.S || j >= a.R || a.mask_kind == EVOATTN_MASK_NONE) return 0u;
-    const long long mi = (long long)b * a.smask.a + (long long)s * a.smask.b + (long long)j * a.smask.c;
-    if (a.mask_kind == EVOATTN_MASK_BOOL) return reinterpret_cast<const unsigned char*>(a.mask)[mi];
-    if (a.mask_kind == EVOATTN_MASK_ADD_F32) return reinterpret_cast<const uint32_t*>(a.mask)[mi];
-    return reinterpret_cast<const uint16_t*>(a.mask)[mi];
-  };
-  // ... and its meaning
-  auto mask_decode = [&](uint32_t raw, int s, int j) -> float {
-    if (s >= a.S || j >= a.R) return -FLT_MAX;
-    if (a.mask_kind == EVOATTN_MASK_NONE) return (MASKMODE == MASK_MIN) ? FLT_MAX : 0.f;
-    if (MASKMODE == MASK_MIN) return raw ? FLT_MAX : -FLT_MAX;
-    if (a.mask_kind == EVOATTN_MASK_ADD_F32) return __uint_as_float(raw);
-    const uint16_t h16 = (uint16_t)raw;
-    return to_float<T>(*reinterpret_cast<const T*>(&h16));
-  };
-
-  if (tid == 0) *abort_flag = (a.status && *reinterpret_cast<volatile int*>(a.status) != 0) ? 1 : 0;
-  __syncthreads();
-  if (*abort_flag) return;
-
-  if (tid == 0) {
-    mbar_init(bar_ld, 1); mbar_init(bar_ld + 1, 1); mbar_init(bar_sdp, 1); mbar_init(bar_sdp + 1, 1);
-    mbar_init(bar_out, 1);
-    mbar_init(bar_cdone, 8);   // one arrival per compute warp
-    mbar_init(bar_sread, 4); mbar_init(bar_sread + 1, 4);
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_bfull + i, 1); mbar_init(bar_bempty + i, 4); }
-    fence_mbar_init();
-    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
-    if (has_bias) prefetch_tmap(&tmB);
-  }
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
-  }
-  {
-    const StepId d0 = decode(0);  // the first item's mask; later items are staged by the compute warps
-    for (int t = tid; t < G * BT; t += 384) sMask[t] = mask_of(d0.b, d0.s + t / BT, d0.j0 + (t % BT));
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-
-  if (warp >= 8) {
-    setmaxnreg_dec<24>();
-    if (warp == 8) {
-      const uint32_t leader = (lane == 0) ? 1u : 0u;  // the lane that issues; everything else is warp-uniform
-      // =============================== control: TMA + MMA ===============================
-      constexpr uint32_t kIdescS = make_idesc(kBf16, false, false, BT, BT);  // S, dP: K-major operands
-      constexpr uint32_t kIdescT = make_idesc(kBf16, true, true, BT, DP);    // dV, dK: A = P^T / dS^T (MN-major)
-      constexpr uint32_t kIdescQ = make_idesc(kBf16, false, true, BT, DP);   // dQ: A = dS K-major, B = K MN-major
-      constexpr uint32_t kHiOp = static_cast<uint32_t>(make_sdesc_const(16, 8 * RB, SWZ) >> 32);
-      constexpr uint32_t kHiPS = static_cast<uint32_t>(make_sdesc_const(16, 1024, SWZ_128B) >> 32);
-      constexpr uint32_t kLoLbo = static_cast<uint32_t>(make_sdesc_const(16, 0, 0) & 0xffffffffu);
-      constexpr uint32_t kLoLboT = static_cast<uint32_t>(make_sdesc_const(BT * 128, 0, 0) & 0xffffffffu);
-      const uint32_t st_lo = smem_u32(smem + L::offStage) >> 4;
-      const uint32_t p_lo0 = smem_u32(sP) >> 4, ds_lo0 = smem_u32(sDS) >> 4;
-
-      auto load_step = [&](int n) {
-        const StepId d = decode(n);
-        const int buf = n & 1;
-        uint8_t* dst = smem + L::offStage + buf * L::kStage;
-        mbar_expect_tx_if(leader, bar_ld + buf, L::kStage);
-        tma_load_5d_if(leader, dst, &tmQ, bar_ld + buf, 0, d.it * BT, d.s, d.h, d.b);
-        tma_load_5d_if(leader, dst + L::kTile, &tmDO, bar_ld + buf, 0, d.it * BT, d.s, d.h, d.b);
-        tma_load_5d_if(leader, dst + 2 * L::kTile, &tmK, bar_ld + buf, 0, d.j0, d.s, d.h, d.b);
-        tma_load_5d_if(leader, dst + 3 * L::kTile, &tmV, bar_ld + buf, 0, d.j0, d.s, d.h, d.b);
-      };
-      // S and dP of step n for the 64 key columns of warpgroup `half` (its own accumulator columns,
-      // its own barrier): a warpgroup's half can be issued as soon as that warpgroup has read the
-      // previous step's, half a step before the other operands of the step are due.
-      constexpr uint32_t kIdescH = make_idesc(kBf16, false, false, BT, BT / 2);
-      auto issue_s_dp = [&](int n, int half) {
-        const int buf = n & 1;
-        const uint32_t base = (st_lo + buf * (L::kStage >> 4)) | kLoLbo;
-        const uint32_t qa = base, da = base + (L::kTile >> 4),
-                       ka = base + 2 * (L::kTile >> 4) + half * ((BT / 2) * RB >> 4),
-                       va = base + 3 * (L::kTile >> 4) + half * ((BT / 2) * RB >> 4);
-#pragma unroll
-        for (int kk = 0; kk < DP / 16; ++kk)
-          mma_ss_if(leader, tmem + colS + half * (BT / 2), pack_desc(qa + kk * 2, kHiOp), pack_desc(ka + kk * 2, kHiOp),
-                    kIdescH, kk > 0 ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < DP / 16; ++kk)
-          mma_ss_if(leader, tmem + colDP + half * (BT / 2), pack_desc(da + kk * 2, kHiOp), pack_desc(va + kk * 2, kHiOp),
-                    kIdescH, kk > 0 ? 1u : 0u);
-        mma_commit_if(leader, bar_sdp + half);
-      };
-      auto issue_out = [&](int n) {
-        const int buf = n & 1, nn = n % SPI, g = nn % G;
-        const uint32_t first = (nn < G) ? 0u : 1u;  // the item's first query tile overwrites the accumulators
-        const uint32_t base = (st_lo + buf * (L::kStage >> 4)) | kLoLbo;
-        const uint32_t qa = base, da = base + (L::kTile >> 4), ka = base + 2 * (L::kTile >> 4);
-        const uint32_t p_lo = p_lo0 + buf * (L::kPS >> 4), ds_lo = ds_lo0 + buf * (L::kPS >> 4);
-        // dV_j[s] += P^T dO_i : A = P read MN-major (M = j); K runs over the 128 query rows
-#pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)
-          mma_ss_if(leader, tmem + colDV + g * DP, pack_desc((p_lo + kk * 128) | kLoLboT, kHiPS), pack_desc(da + kk * RB, kHiOp),
-                 kIdescT, (kk > 0) ? 1u : first);
-        // dK_j[s] += dS^T Q_i
-#pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)
-          mma_ss_if(leader, tmem + colDK + g * DP, pack_desc((ds_lo + kk * 128) | kLoLboT, kHiPS), pack_desc(qa + kk * RB, kHiOp),
-                 kIdescT, (kk > 0) ? 1u : first);
-        // dQ_i[s] partial = dS K_j : A = dS K-major (K runs over the 128 keys)
-#pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)
-          mma_ss_if(leader, tmem + colDQ, pack_desc((ds_lo + (kk >> 2) * (BT * 128 >> 4) + (kk & 3) * 2) | kLoLbo, kHiPS),
-                 pack_desc(ka + kk * RB, kHiOp), kIdescQ, kk > 0 ? 1u : 0u);
-        mma_commit_if(leader, bar_out);
-      };
-
-      load_step(0);
-      if (total_steps > 1) load_step(1);
-      mbar_wait(bar_ld, 0, abort_flag, a.status, DEV_TIMEOUT_TMA);
-      tc_fence_after();
-      issue_s_dp(0, 0);
-      issue_s_dp(0, 1);
-      for (int n = 0; n < total_steps; ++n) {
-        if (n + 1 < total_steps) {
-          mbar_wait(bar_ld + ((n + 1) & 1), ((n + 1) >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            mbar_wait(bar_sread + half, n & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
-            tc_fence_after();
-            issue_s_dp(n + 1, half);
-          }
-        }
-        mbar_wait(bar_cdone, n & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
-        tc_fence_after();
-        issue_out(n);  // runs underneath step n+1's arithmetic
-        if (n + 2 < total_steps) {
-          // the stage of step n is free once its MMAs have completed
-          mbar_wait(bar_out, n & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
-          load_step(n + 2);
-        }
-      }
-    } else if (warp <= 10 && has_bias) {
-      // ============ pair-bias loaders: warp 9 feeds warpgroup 0, warp 10 warpgroup 1 ============
-      // The warpgroup's buffer holds the bias of one block of 32 key columns (two 128x16 chunks,
-      // which is all the shared memory left): a block is requested as soon as the one before it has
-      // been read into registers, and lands while that one is being worked on.
-      const uint32_t leader = (lane == 0) ? 1u : 0u;
-      const int wgc = warp - 9;
-      uint32_t blk = 0;
-      for (int n = 0; n < total_steps; ++n) {
-        const StepId d = decode(n);
-        for (int c = 0; c < 2; ++c, ++blk) {
-          mbar_wait(bar_bempty + wgc, (blk & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
-          mbar_expect_tx_if(leader, bar_bfull + wgc, 2 * L::kBiasChunk);
-#pragma unroll
-          for (int q = 0; q < 2; ++q)
-            tma_load_4d_if(leader, sB + (wgc * 2 + q) * L::kBiasChunk, &tmB, bar_bfull + wgc,
-                           d.j0 + wgc * 64 + c * 32 + q * 16, d.it * BT, d.h, d.b);
-        }
-      }
-    }
-  } else {
-    // =============================== compute warps ===============================
-    setmaxnreg_inc<240>();
-    const int wg = warp >> 2;
-    const int row = (warp & 3) * 32 + lane;
-    const uint32_t t_lane = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const float scale = a.scale;
-    const float inv_r = 1.f / (float)a.R;
-    const F2 scale2 = f2_make(scale, scale), l2e2 = f2_make(kLog2e, kLog2e);
-    uint32_t bseq = 0;
-
-    // The dQ partial of a step leaves TMEM at the end of the following step (its MMAs ran
-    // underneath that step's arithmetic) and is added to the fp32 accumulator in global memory
-    // four floats at a time during the step after that: reductions drain at about 16 bytes per
-    // clock, and a warp that issues them back to back stalls until they have drained.
-    uint32_t qr[HALF_D];       // the partial taken out of TMEM last
-    float* dq_pend = nullptr;  // its destination (null for a row that does not exist)
-    auto take_dq = [&](int n, float* dst) {
-      mbar_wait(bar_out, n & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
-      tc_fence_after();
-      tmem_ld<HALF_D>(t_lane + colDQ + wg * HALF_D, qr);
-      tmem_wait_ld();
-      dq_pend = dst;
-    };
-    auto add_dq = [&](int d4) {  // one group of four floats of the pending partial
-      if (d4 < HALF_D / 4 && dq_pend != nullptr && wg * HALF_D + d4 * 4 < a.D)
-        red_add_v4(dq_pend + d4 * 4, __uint_as_float(qr[d4 * 4]), __uint_as_float(qr[d4 * 4 + 1]),
-                   __uint_as_float(qr[d4 * 4 + 2]), __uint_as_float(qr[d4 * 4 + 3]));
-    };
-
-    // dK, dV of row-group slot g (MSA row s of (b,h), keys j0..): TMEM -> registers -> global
-    auto drain_dkdv = [&](int b, int h, int s, int j0, int g) {
-      const int j = j0 + row;
-      uint32_t kr[HALF_D], vr[HALF_D];
-      tmem_ld<HALF_D>(t_lane + colDK + g * DP + wg * HALF_D, kr);
-      tmem_ld<HALF_D>(t_lane + colDV + g * DP + wg * HALF_D, vr);
-      tmem_wait_ld();
-      if (j < a.R && s < a.S) {
-        T* kd = reinterpret_cast<T*>(a.dk) + off4(a.sdk, b, h, s, j) + wg * HALF_D;
-        T* vd = reinterpret_cast<T*>(a.dv) + off4(a.sdv, b, h, s, j) + wg * HALF_D;
-#pragma unroll
-        for (int d8 = 0; d8 < HALF_D / 8; ++d8) {
-          if (wg * HALF_D + d8 * 8 < a.D) {
-            uint4 pk, pv;
-            pk.x = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 0]) * scale, __uint_as_float(kr[d8 * 8 + 1]) * scale);
-            pk.y = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 2]) * scale, __uint_as_float(kr[d8 * 8 + 3]) * scale);
-            pk.z = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 4]) * scale, __uint_as_float(kr[d8 * 8 + 5]) * scale);
-            pk.w = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 6]) * scale, __uint_as_float(kr[d8 * 8 + 7]) * scale);
-            pv.x = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 0]), __uint_as_float(vr[d8 * 8 + 1]));
-            pv.y = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 2]), __uint_as_float(vr[d8 * 8 + 3]));
-            pv.z = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 4]), __uint_as_float(vr[d8 * 8 + 5]));
-            pv.w = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 6]), __uint_as_float(vr[d8 * 8 + 7]));
-            *reinterpret_cast<uint4*>(kd + d8 * 8) = pk;
-            *reinterpret_cast<uint4*>(vd + d8 * 8) = pv;
-          }
-        }
-      }
-    };
-
-    // log-sum-exp and delta of this thread's query row for a step (rows that do not exist get a
-    // huge lse so that their P is exactly 0)
-    float lse_next = 1e30f, delta_next = 0.f;
-    auto load_row_stats = [&](const StepId& d, bool in_range) {
-      // predicated loads: a select on the loaded value would wait for the load right here
-      const int i = d.it * BT + row;
-      const bool ok = in_range && i < a.R && d.s < a.S;
-      const long long ri = (((long long)d.b * a.H + d.h) * a.S + d.s) * a.R + i;
-      lse_next = ldg_f32_if(a.lse + ri, ok, 1e30f);
-      delta_next = ldg_f32_if(a.delta + ri, ok, 0.f);
-    };
-    // The compute warps step their position instead of decoding it: the divisions of `decode` are a
-    // dependent chain of several hundred cycles, paid only when an item ends.
-    StepId cur = decode(0);
-    auto advance = [&](const StepId& c, int n) {  // position of step n = the one after c
-      StepId d = c;
-      if (++d.g == G) {
-        d.g = 0;
-        if (++d.it == NT) return decode(n);
-      } 
-      d.s = c.s - c.g + d.g;
-      return d;
-    };
-    load_row_stats(cur, total_steps > 0);
-    float* dq_prev = nullptr;                 // where the previous step's dQ partial goes
-    int pb = 0, ph = 0, ps0 = 0, pj0 = 0;     // the item whose dK/dV still sit in TMEM
-    float bacc[64];
-    bool flush_pending = false;
-
-    for (int step = 0; step < total_steps; ++step) {
-      const StepId nxt = advance(cur, step + 1);
-      const bool more = step + 1 < total_steps;
-      const bool item_ends = (cur.it == NT - 1) && (cur.g == G - 1);
-      const int g = cur.g;
-      const int j0 = cur.j0;
-      if (g == 0) {
-#pragma unroll
-        for (int e = 0; e < 64; ++e) bacc[e] = 0.f;
-      }
-      // Fetched during the previous step.  They are pinned in registers before the next fetch is
-      // issued: the same load instruction reuses its scoreboard slot, and a wait for the old value
-      // placed after the new load would wait for the new one as well.
-      float lse = lse_next, delta = delta_next;
-      asm volatile("" : "+f"(lse), "+f"(delta)::"memory");
-      load_row_stats(nxt, more);  // in flight during this step
-      // the next item's residue mask, fetched under this item's last step (threads 0..255 cover
-      // G*128 = 384 values: one each, a second one for the first 128 threads)
-      float mnext0 = 0.f, mnext1 = 0.f;
-      if (item_ends && more) {
-        mnext0 = mask_of(nxt.b, nxt.s + tid / BT, nxt.j0 + (tid % BT));
-        if (tid < G * BT - 256) mnext1 = mask_of(nxt.b, nxt.s + (tid + 256) / BT, nxt.j0 + ((tid + 256) % BT));
-      }
-      const bool dead = (lse == -FLT_MAX);  // every key of this row was dropped: P is uniform
-      const float nlse = -lse * kLog2e;
-      const F2 nlse2 = f2_make(nlse, nlse), delta2 = f2_make(delta, delta);
-      mbar_wait(bar_sdp + wg, step & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
-      tc_fence_after();
-
-      uint8_t* prow = sP + (step & 1) * L::kPS + wg * (BT * 128) + row * 128;
-      uint8_t* drow = sDS + (step & 1) * L::kPS + wg * (BT * 128) + row * 128;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = wg * 64 + c * 32;
-        uint32_t sr[32], dr[32];
-        tmem_ld32(t_lane + colS + col0, sr);
-        tmem_ld32(t_lane + colDP + col0, dr);
-        tmem_wait_ld();
-        if (c == 1) {  // this warpgroup's S, dP columns are in registers: the next step's may be issued
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_sread + wg);
-        }
-        const float* mrow = sMask + g * BT + col0;
-        // pair bias: my row's 32 floats come as two chunks of 16 (64 bytes each, 64-byte swizzle)
-        float bv[32];
-        if (has_bias) {
-          mbar_wait(bar_bfull + wg, bseq & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
-#pragma unroll
-          for (int h16 = 0; h16 < 2; ++h16) {
-            const uint8_t* brow = sB + (wg * 2 + h16) * L::kBiasChunk + row * 64;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              const float4 f = *reinterpret_cast<const float4*>(brow + ((q4 ^ ((row >> 1) & 3)) << 4));
-              bv[h16 * 16 + q4 * 4 + 0] = f.x; bv[h16 * 16 + q4 * 4 + 1] = f.y;
-              bv[h16 * 16 + q4 * 4 + 2] = f.z; bv[h16 * 16 + q4 * 4 + 3] = f.w;
-            }
-          }
-          // The buffer is handed back only after the loads above have returned: a store that needs
-          // one word of each of them is issued first (an mbarrier arrival does not wait for shared
-          // loads still queued behind this warp's global reductions, and the refill would then
-          // overwrite what they are about to read).
-          *scratch = __float_as_uint(bv[0]) ^ __float_as_uint(bv[4]) ^ __float_as_uint(bv[8]) ^ __float_as_uint(bv[12]) ^
-                     __float_as_uint(bv[16]) ^ __float_as_uint(bv[20]) ^ __float_as_uint(bv[24]) ^ __float_as_uint(bv[28]);
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_bempty + wg);  // one arrival per warp
-          ++bseq;
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) bv[e] = 0.f;
-        }
-        {
-          // thirty-two columns at a time: enough independent work in flight to cover the latencies
-          // of the exponential unit and of shared memory with only two warps per scheduler
-          constexpr int W = 32;
-          float p[W], ds[W];
-          float mkv[W];
-#pragma unroll
-          for (int u = 0; u < W; u += 4) {
-            const float4 mk = *reinterpret_cast<const float4*>(mrow + u);
-            mkv[u] = mk.x; mkv[u + 1] = mk.y; mkv[u + 2] = mk.z; mkv[u + 3] = mk.w;
-          }
-          if (!dead) {
-            float x[W];
-#pragma unroll
-            for (int u = 0; u < W; u += 2)  // x = scale*S + bias, two elements per instruction
-              f2_get(f2_fma(f2_from_bits(sr[u], sr[u + 1]), scale2, f2_make(bv[u], bv[u + 1])), x[u], x[u + 1]);
-#pragma unroll
-            for (int u = 0; u < W; ++u) x[u] = (MASKMODE == MASK_MIN) ? fminf(x[u], mkv[u]) : (x[u] + mkv[u]);
-#pragma unroll
-            for (int u = 0; u < W; u += 2) f2_get(f2_fma(f2_make(x[u], x[u + 1]), l2e2, nlse2), x[u], x[u + 1]);
-#pragma unroll
-            for (int u = 0; u < W; ++u) p[u] = ex2(x[u]);
-#pragma unroll
-            for (int u = 0; u < W; u += 2) {  // dS = P (dP - delta); d_bias_acc += dS
-              const F2 t = f2_mul(f2_make(p[u], p[u + 1]), f2_sub(f2_from_bits(dr[u], dr[u + 1]), delta2));
-              f2_get(t, ds[u], ds[u + 1]);
-              f2_get(f2_add(f2_make(bacc[c * 32 + u], bacc[c * 32 + u + 1]), t), bacc[c * 32 + u], bacc[c * 32 + u + 1]);
-            }
-          } else {
-#pragma unroll
-            for (int u = 0; u < W; ++u) {
-              p[u] = (j0 + col0 + u < a.R) ? inv_r : 0.f;
-              ds[u] = 0.f;  // replaced scores are constants: no gradient flows through them
-            }
-          }
-          if (flush_pending) {
-            // the d_bias reductions issued after the previous step read shared memory at the pace
-            // the reductions drain; this step's first block of arithmetic ran underneath that
-            if ((tid & 127) == 0) tma_wait_group_read0();
-            named_bar_sync(1 + wg, 128);
-            flush_pending = false;
-          }
-#pragma unroll
-          for (int c8 = 0; c8 < W / 8; ++c8) {
-            uint4 pk, dk;
-            pk.x = Pack2<T>::pack(p[c8 * 8 + 0], p[c8 * 8 + 1]); pk.y = Pack2<T>::pack(p[c8 * 8 + 2], p[c8 * 8 + 3]);
-            pk.z = Pack2<T>::pack(p[c8 * 8 + 4], p[c8 * 8 + 5]); pk.w = Pack2<T>::pack(p[c8 * 8 + 6], p[c8 * 8 + 7]);
-            dk.x = Pack2<T>::pack(ds[c8 * 8 + 0], ds[c8 * 8 + 1]); dk.y = Pack2<T>::pack(ds[c8 * 8 + 2], ds[c8 * 8 + 3]);
-            dk.z = Pack2<T>::pack(ds[c8 * 8 + 4], ds[c8 * 8 + 5]); dk.w = Pack2<T>::pack(ds[c8 * 8 + 6], ds[c8 * 8 + 7]);
-            const int chunk16 = ((c * 4 + c8) ^ (row & 7)) << 4;
-            *reinterpret_cast<uint4*>(prow + chunk16) = pk;
-            *reinterpret_cast<uint4*>(drow + chunk16) = dk;
-          }
-          add_dq(c * 2);
-          add_dq(c * 2 + 1);
-        }
-      }
-      // the previous step's dQ partial must be out of TMEM before the control warp may issue
-      // this step's dQ MMA
-      if (step > 0) take_dq(step - 1, dq_prev);
-      // dK/dV of the previous item's slot g: complete (the wait above covers every earlier MMA),
-      // and about to be overwritten by this step's MMAs
-      if (cur.it == 0 && step >= SPI) drain_dkdv(pb, ph, ps0 + g, pj0, g);
-      tc_fence_before();
-      fence_async_shared();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_cdone);  // P, dS of this step are in shared memory; S, dP, dQ have been read
-      {
-        const int i = cur.it * BT + row;
-        dq_prev = (i < a.R && cur.s < a.S)
-                      ? dq_acc + ((((long long)cur.b * a.H + cur.h) * a.S + cur.s) * a.R + i) * a.D + wg * HALF_D
-                      : nullptr;
-      }
-
-      // One reduction of this CTA's d_bias tile (i-tile, j-tile) after the group's last row: each
-      // warpgroup stages its 128x64 fp32 half as two 128x32 boxes (128-byte-swizzled rows) in the
-      // halves of the P and dS buffers that only this warpgroup will write at the next step (their
-      // last readers, the MMAs of step `step-1`, have completed: their dQ partial was folded
-      // above) and adds them to global memory with two bulk tensor reductions.
-      if (g == G - 1 && a.dbias != nullptr) {
-        const int nb = (step + 1) & 1;
-        uint8_t* stage0 = sP + nb * L::kPS + wg * (BT * 128);
-        uint8_t* stage1 = sDS + nb * L::kPS + wg * (BT * 128);
-#pragma unroll
-        for (int bx = 0; bx < 2; ++bx)
-#pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4)
-            *reinterpret_cast<float4*>((bx == 0 ? stage0 : stage1) + row * 128 + ((q4 ^ (row & 7)) << 4)) =
-                make_float4(bacc[bx * 32 + q4 * 4], bacc[bx * 32 + q4 * 4 + 1], bacc[bx * 32 + q4 * 4 + 2],
-                            bacc[bx * 32 + q4 * 4 + 3]);
-        fence_async_shared();
-        named_bar_sync(1 + wg, 128);
-        if ((tid & 127) == 0) {
-          tma_reduce_add_4d(&tmDB, stage0, j0 + wg * 64, cur.it * BT, cur.h, cur.b);
-          tma_reduce_add_4d(&tmDB, stage1, j0 + wg * 64 + 32, cur.it * BT, cur.h, cur.b);
-          tma_commit_group();
-        }
-        flush_pending = true;  // the staging halves are this warpgroup's P/dS halves of the next step
-      }
-
-      if (item_ends) {
-        pb = cur.b; ph = cur.h; ps0 = cur.s - g; pj0 = j0;
-        if (more) {
-          named_bar_sync(3, 256);  // every compute warp has read this item's mask for the last time
-          sMask[tid] = mnext0;
-          if (tid < G * BT - 256) sMask[tid + 256] = mnext1;
-          named_bar_sync(3, 256);
-        }
-      }
-      cur = nxt;
-    }
-
-    if (total_steps > 0) {
-#pragma unroll
-      for (int d4 = 0; d4 < 4; ++d4) add_dq(d4);
-      take_dq(total_steps - 1, dq_prev);  // also the point where every MMA of this CTA has completed
-#pragma unroll
-      for (int d4 = 0; d4 < 4; ++d4) add_dq(d4);
-      if (a.dbias != nullptr && (tid & 127) == 0) tma_wait_group0();
-      for (int g = 0; g < G; ++g) drain_dkdv(pb, ph, ps0 + g, pj0, g);
-    }
-  }
-
-  if (*abort_flag) {
-    const long long t0 = clock64();
-    while (clock64() - t0 < 200000) {}
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
-}
-
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <class T, int DP>
@@ -1054,8 +496,7 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (!make_qkv_map(&tdo, a.d_o, a.sdo, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   CUtensorMap tdb;
   if (a.bias) {
-    // 128x16 chunks for the eight-warp kernel (D <= 16), 128x32 blocks for the others
-    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, (DP <= 16) ? 16 : 32)) return EVOATTN_ERR_CUDA;
+    if (!make_bias_map(&tb, a.bias, a.sbias, a.B, a.H, a.R, BT, 32)) return EVOATTN_ERR_CUDA;
     const Str3 dense{(long long)a.H * a.R * a.R, (long long)a.R * a.R, (long long)a.R};
     if (!a.dbias) tdb = tq;  // the bias needs no gradient
     else if (!make_bias_map(&tdb, a.dbias, dense, a.B, a.H, a.R, BT, 32)) return EVOATTN_ERR_CUDA;
@@ -1071,23 +512,7 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
 
   const int NT = (a.R + BT - 1) / BT;
   const bool add = a.mask_kind == EVOATTN_MASK_ADD_F32 || a.mask_kind == EVOATTN_MASK_ADD_SAME;
-  if constexpr (DP <= 32) {
-    using W = WsSmem<DP>;
-    // one persistent CTA per SM (shared memory and TMEM allow no more) over all items
-    const long long items = (long long)a.B * a.H * NT * ((a.S + W::G - 1) / W::G);
-    if (items > 0x7fffffffLL / (W::G * NT)) return EVOATTN_ERR_SHAPE;
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-      return EVOATTN_ERR_CUDA;
-    const long long ctas = items < sms ? items : sms;
-    {
-      auto kern = add ? evo_bwd_ws_kernel<T, DP, MASK_ADD> : evo_bwd_ws_kernel<T, DP, MASK_MIN>;
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)W::bytes) != cudaSuccess)
-        return EVOATTN_ERR_CUDA;
-      kern<<<(unsigned)ctas, 384, W::bytes, st>>>(a, dq_acc, (int)items, tq, tk, tv, tdo, tb, tdb);
-    }
-  } else {
+  {
     const long long ctas = (long long)a.B * a.H * NT * ((a.S + G - 1) / G);
     auto kern = add ? evo_bwd_sm100_kernel<T, DP, MASK_ADD> : evo_bwd_sm100_kernel<T, DP, MASK_MIN>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::bytes) != cudaSuccess)
@@ -1102,9 +527,6 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
 
 template <class T>
 int launch_d(const Args& a, void* ws, size_t ws_bytes, cudaStream_t st, int* launches) {
-#ifndef EVO_D16_T
-  if (a.D <= 16) return launch_t<T, 16>(a, ws, ws_bytes, st, launches);
-#endif
   if (a.D <= 32)  // the kernel with transposed score tiles (bwdt_sm100.cu)
     return launch_sm100_bwdt(std::is_same<T, __nv_bfloat16>::value ? EVOATTN_BF16 : EVOATTN_FP16, a, ws, ws_bytes, st,
                              launches);
@@ -1121,10 +543,7 @@ bool sm100_bwd_supported(int dtype, const Args& a) {
 }
 
 size_t sm100_bwd_workspace_bytes(int, const Args& a) {
-#ifdef EVO_D16_T
   if (a.D <= 32) return sm100_bwdt_workspace_bytes(a);
-#endif
-  if (a.D > 16 && a.D <= 32) return sm100_bwdt_workspace_bytes(a);
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;
   const size_t wide_bytes = (a.bias && a.bias16) ? (size_t)a.B * a.H * a.R * a.R * sizeof(float) : 0;
   return align_up(rows * sizeof(float), 256) + align_up(rows * a.D * sizeof(float), 256) + wide_bytes;

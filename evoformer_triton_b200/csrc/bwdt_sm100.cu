@@ -36,12 +36,16 @@ namespace {
 using namespace ptx;
 
 constexpr int BT = 128;   // tile edge (queries and keys)
-constexpr int HT = 64;    // queries per mini-step
+constexpr int HT = 64;    // queries per half of a step (one warp group)
+constexpr int QT = 32;    // queries per quarter of a step
+// S^T / dP^T buffers per half: 1 = one of 64 queries, 2 = one per quarter (measured slower: forty
+// smaller MMAs per step instead of thirty-two, and twice the hand-overs)
+constexpr int kSub = 1;
 constexpr int G = 3;      // MSA rows per work item
 constexpr int kCW = 16;   // compute warps
 constexpr int kThreadsT = 640;  // 16 compute + 4 service warps, five warps per scheduler
-constexpr int kComputeRegs = 112, kServiceRegs = 24;  // after setmaxnreg; the launch-time pool must hold their sum
-constexpr int kStages = 2;
+constexpr int kComputeRegs = 112, kServiceRegs = 32;  // after setmaxnreg; the launch-time pool must hold their sum
+constexpr int kStages = 2;  // (three or four stages measured no faster: the loads are not what a step waits for)
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int DP>
@@ -59,7 +63,7 @@ struct SmemT {
   static constexpr int offBias = offDS + kDS;
   static constexpr int offOut = offBias + kBias;
   static constexpr int offBars = offOut + kCW * kOutWarp;
-  static constexpr size_t bytes = offBars + 512 + 1024;  // 25 barriers and three words
+  static constexpr size_t bytes = offBars + 512 + 1024;  // 64 barrier slots (see the kernel), and the alignment slack
   static_assert(offDS % 1024 == 0 && kStage % 1024 == 0, "swizzled tiles need 1024-byte alignment");
   static_assert(bytes <= 232448, "shared memory budget of one CTA");
 };
@@ -178,10 +182,10 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
   const uint32_t bars_s = smem_u32(bars);
   const Bar kv_full{bars_s + 8 * 0};     // [G] K and V of row g of the current item landed
   const Bar kv_empty{bars_s + 8 * 3};    // [G] ... and every MMA that reads them has completed
-  const Bar st_full{bars_s + 8 * 6};     // [2] Q, dO and the statistics vectors of a step landed
-  const Bar st_empty{bars_s + 8 * 8};    // [2] ... the step's last dV/dK MMAs have completed
-  const Bar sd_full{bars_s + 8 * 10};    // [2] S^T and dP^T of half h of a step are in TMEM buffer h
-  const Bar cdone{bars_s + 8 * 12};      // [2] the warps of half h have P^T and dS^T of a step in TMEM (for the dV/dK MMAs)
+  const Bar st_full{bars_s + 8 * 32};     // [2] Q, dO and the statistics vectors of a step landed
+  const Bar st_empty{bars_s + 8 * 40};    // [2] ... the step's last dV/dK MMAs have completed
+  const Bar sd_full{bars_s + 8 * 48};    // [2][2] S^T and dP^T of quarter (h, sub) of a step are in TMEM
+  const Bar cdone{bars_s + 8 * 52};      // [2][2] the warps of half h have P^T and dS^T of quarter sub in TMEM (for the dV/dK MMAs)
   const Bar sdone{bars_s + 8 * 23};      // [2] ... and have stored their half of dS in shared memory (for the dQ MMAs)
   const Bar b_full{bars_s + 8 * 14};     // [2] half h (64 queries) of the pair-bias tile landed
   const Bar b_done{bars_s + 8 * 16};     // [2] ... has been read for the last time
@@ -232,9 +236,9 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
 
   if (tid == 0) {
     for (int i = 0; i < G; ++i) { mbar_init(bars + 0 + i, 1); mbar_init(bars + 3 + i, 3); }  // kv_full; kv_empty: three MMA warps read K/V
-    for (int i = 0; i < kStages; ++i) { mbar_init(bars + 6 + i, 1); mbar_init(bars + 8 + i, 2); }  // st_full, st_empty
+    for (int i = 0; i < kStages; ++i) { mbar_init(bars + 32 + i, 1); mbar_init(bars + 40 + i, 2); }  // st_full, st_empty
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bars + 10 + i, 2); mbar_init(bars + 12 + i, kCW / 2);  // sd_full, cdone
+      for (int q = 0; q < 2; ++q) { mbar_init(bars + 48 + 2 * i + q, 2); mbar_init(bars + 52 + 2 * i + q, kCW / 2); }  // sd_full, cdone
       mbar_init(bars + 14 + i, 1); mbar_init(bars + 16 + i, kCW / 2);  // b_full, b_done
       mbar_init(bars + 19 + i, 1);                                     // dq_full
       mbar_init(bars + 23 + i, kCW / 2);                               // sdone
@@ -270,7 +274,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       // leader lane in a converged warp).
       const bool isA = (warp == kCW);
       if (lane == 0) {
-      constexpr uint32_t kIdescSD = make_idesc(kBf16, false, false, BT, HT);   // S^T, dP^T: K-major operands, N = 64
+      constexpr uint32_t kIdescSD = make_idesc(kBf16, false, false, BT, HT / kSub);   // S^T, dP^T: K-major operands, N = 64 or 32
       constexpr uint32_t kIdescOut = make_idesc(kBf16, false, true, BT, DP);   // dV, dK: A from TMEM, B MN-major
       constexpr uint32_t kHiOp = static_cast<uint32_t>(make_sdesc_const(16, 8 * RB, SWZ) >> 32);
       constexpr uint32_t kLoLbo = static_cast<uint32_t>(make_sdesc_const(16, 0, 0) & 0xffffffffu);
@@ -282,45 +286,70 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       const uint32_t col_in0 = isA ? colS0 : colDP0, col_in1 = isA ? colS1 : colDP1;
       const uint32_t col_acc = isA ? colDV : colDK;
 
-      auto issue_in = [&](int n, int h) {  // S^T (warp 16) or dP^T (warp 17) of half h of step n
-        const int nn = n % SPI, g = nn % G, it = nn / G, stg = n % kStages;
-        if (h == 0) {
-          mbar_wait(st_full + stg, (n / kStages) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
-          if (it == 0) mbar_wait(kv_full + g, (n / SPI) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
-          tc_fence_after();
-        }
-        const uint32_t ka = (kv_lo + (2 * g) * (L::kTile >> 4)) | kLoLbo;
-        const uint32_t qa = (in_lo + stg * (L::kStage >> 4) + h * ((HT * RB) >> 4)) | kLoLbo;
-        const uint32_t tD = tmem + (h ? col_in1 : col_in0);
-        static_assert(DP == 32, "two K slices");
-        // (the second commit: the item's last read of this warp's K or V tile of row g)
-        mma_ss_x2_commit(tD, ka, qa, kHiOp, 2, kIdescSD, (sd_full + h).a, (h == 1 && it == NT - 1) ? (kv_empty + g).a : 0u);
+      // Position of a step inside this CTA's list, advanced without divisions: row g of the group,
+      // query tile it, ring stage and the parities of the stage ring and of the item.
+      struct Pos { int g, it; uint32_t stg, ring_par, item_par; };
+      auto after = [&](Pos p) {
+        if (++p.g == G) { p.g = 0; if (++p.it == NT) { p.it = 0; p.item_par ^= 1u; } }
+        if (++p.stg == (uint32_t)kStages) { p.stg = 0; p.ring_par ^= 1u; }
+        return p;
       };
-      auto issue_out = [&](int n, int h) {  // dV_j[g] += P^T dO_i (warp 16) or dK_j[g] += dS^T Q_i (warp 17)
-        const int nn = n % SPI, g = nn % G, it = nn / G, stg = n % kStages;
-        const uint32_t first = (it == 0 && h == 0) ? 0u : 1u;  // the item's first half-step of row g overwrites
-        const uint32_t ba = (out_lo + stg * (L::kStage >> 4) + (4 * h) * kRowBlk) | kLoLbo;
-        const uint32_t tA = tmem + (h ? col_in1 : col_in0);
-        // A = 16 queries of P^T / dS^T (8 packed TMEM columns), B = their dO / Q rows
-        mma_ts_x4(tmem + col_acc + g * DP, tA, ba, kHiOp, kRowBlk, kIdescOut, first);
-        if (h == 1) mma_commit_if(1u, st_empty + stg);
+      constexpr int QB = HT / kSub;  // queries per S^T / dP^T buffer
+      // Everything an MMA group needs is computed before the wait it follows: this thread shares its
+      // scheduler with four arithmetic warps, so every instruction between the wake-up and the MMA is
+      // paid several times over, and it sits on the critical path of the half that waits for it.
+      auto issue_in = [&](const Pos& p, uint32_t ka, uint32_t qb, int h, int sub) {
+        mma_ss_x2_commit(tmem + (h ? col_in1 : col_in0) + sub * QB, ka, qb + (h * HT + sub * QB) * (RB >> 4), kHiOp, 2, kIdescSD,
+                         (sd_full + (2 * h + sub)).a, (h == 1 && sub == kSub - 1 && p.it == NT - 1) ? (kv_empty + p.g).a : 0u);
       };
-
+      Pos cur{0, 0, 0u, 0u, 0u};
       if (total_steps > 0) {
-        issue_in(0, 0);
-        issue_in(0, 1);
+        mbar_wait(st_full + 0, 0, abort_s, a.status, DEV_TIMEOUT_TMA);
+        mbar_wait(kv_full + 0, 0, abort_s, a.status, DEV_TIMEOUT_TMA);
+        tc_fence_after();
+        const uint32_t ka = (kv_lo + 0) | kLoLbo, qb = in_lo | kLoLbo;
+#pragma unroll
+        for (int sub = 0; sub < kSub; ++sub) { issue_in(cur, ka, qb, 0, sub); issue_in(cur, ka, qb, 1, sub); }
       }
       for (int n = 0; n < total_steps; ++n) {
+        const Pos nxt = after(cur);
+        const bool more = n + 1 < total_steps;
+        // this step: dV_j[g] += P^T dO_i (warp 16) or dK_j[g] += dS^T Q_i (warp 17);
+        // A = 16 queries of P^T / dS^T (8 packed TMEM columns), B = their dO / Q rows
+        const uint32_t acc = tmem + col_acc + cur.g * DP;
+        const uint32_t ob = (out_lo + cur.stg * (L::kStage >> 4)) | kLoLbo;
+        const uint32_t first0 = (cur.it == 0) ? 0u : 1u;  // the item's first MMA of row g overwrites
+        const uint32_t st_empty_bar = (st_empty + (int)cur.stg).a;
+        // next step: S^T = K_j Q_i^T (warp 16) or dP^T = V_j dO_i^T (warp 17) into the buffer just read
+        const uint32_t ka = (kv_lo + (2 * nxt.g) * (L::kTile >> 4)) | kLoLbo;
+        const uint32_t qb = (in_lo + nxt.stg * (L::kStage >> 4)) | kLoLbo;
+        const uint32_t st_full_bar = (st_full + (int)nxt.stg).a, kv_full_bar = (kv_full + nxt.g).a;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          mbar_wait(cdone + h, n & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
-          if (isA) { TR(1, 3 * h) }
-          tc_fence_after();
-          issue_out(n, h);
-          if (isA) { TR(1, 3 * h + 1) }
-          if (n + 1 < total_steps) issue_in(n + 1, h);
-          if (isA) { TR(1, 3 * h + 2) }
+        for (int sub = 0; sub < kSub; ++sub) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            mbar_wait(cdone + (2 * h + sub), n & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
+            if (isA) { TR(1, 6 * sub + 3 * h) }
+            tc_fence_after();
+            const uint32_t tA = tmem + (h ? col_in1 : col_in0) + sub * QB;
+            const uint32_t ba = ob + (4 * h + (4 / kSub) * sub) * kRowBlk;
+            const uint32_t first = (h == 0 && sub == 0) ? first0 : 1u;
+            if constexpr (kSub == 1) mma_ts_x4(acc, tA, ba, kHiOp, kRowBlk, kIdescOut, first);
+            else mma_ts_x2(acc, tA, ba, kHiOp, kRowBlk, kIdescOut, first);
+            if (h == 1 && sub == kSub - 1) mma_commit_if_s(1u, st_empty_bar);
+            if (isA) { TR(1, 6 * sub + 3 * h + 1) }
+            if (more) {
+              if (h == 0 && sub == 0) {
+                mbar_wait_s(st_full_bar, nxt.ring_par, abort_s, a.status, DEV_TIMEOUT_TMA);
+                if (nxt.it == 0) mbar_wait_s(kv_full_bar, nxt.item_par, abort_s, a.status, DEV_TIMEOUT_TMA);
+                tc_fence_after();
+              }
+              issue_in(nxt, ka, qb, h, sub);
+            }
+            if (isA) { TR(1, 6 * sub + 3 * h + 2) }
+          }
         }
+        cur = nxt;
       }
       }  // lane 0
     } else if (warp == kCW + 2) {
@@ -337,24 +366,23 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       // The bias tile (i, j) is the same for the G rows of a group; each half (64 queries) is loaded
       // for the group's first step and replaced as soon as the warps of that half have read it for
       // the last time.
-      auto load_bias = [&](int t, int h) {
-        const StepT d = decode(t * G);
-        if (lane == 0) {
-          mbar_expect_tx(b_full + h, HT * kBRow);
-          tma_load_4d_s(sBias_s + h * (HT * kBRow), &tmB, (b_full + h).a, d.j0, d.it * BT + h * HT, d.h, d.b);
-        }
+      auto load_bias = [&](const StepT& d, int h) {
+        mbar_expect_tx(b_full + h, HT * kBRow);
+        tma_load_4d_s(sBias_s + h * (HT * kBRow), &tmB, (b_full + h).a, d.j0, d.it * BT + h * HT, d.h, d.b);
       };
       const int tiles = my_items * NT;
-      if (has_bias && tiles > 0) { load_bias(0, 0); load_bias(0, 1); }
+      if (has_bias && tiles > 0) { const StepT d0 = decode(0); load_bias(d0, 0); load_bias(d0, 1); }
+      int g = 0, it = 0, t = 0;  // row of the group, query tile, running (item, query tile) index
       for (int n = 0; n < total_steps; ++n) {
-        const int nn = n % SPI, g = nn % G, it = nn / G, t = n / G;
         const bool turn = has_bias && g == G - 1 && t + 1 < tiles;  // the group's last step: the halves come back
+        StepT nb = StepT{0, 0, 0, 0, 0, 0};
+        if (turn) nb = decode((t + 1) * G);  // (divisions: before the waits, not between them)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           mbar_wait(sdone + h, n & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
           if (turn) {
             mbar_wait(b_done + h, t & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
-            load_bias(t + 1, h);
+            load_bias(nb, h);
           }
         }
         TR(2, 0)
@@ -366,6 +394,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
         mma_commit_if(1u, ds_empty);
         if (it == NT - 1) mma_commit_if(1u, kv_empty + g);
         TR(2, 2)
+        if (++g == G) { g = 0; ++t; if (++it == NT) it = 0; }
       }
       }  // lane 0
     } else {
@@ -411,7 +440,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
     const int q4 = warp & 3, cb2 = (warp >> 2) & 1, H = warp >> 3;
     const int jrow = q4 * 32 + lane;
     const uint32_t t_lane = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
-    const uint32_t cS = t_lane + (H ? colS1 : colS0) + 32 * cb2, cP = t_lane + (H ? colDP1 : colDP0) + 32 * cb2;
+    const uint32_t cS = t_lane + (H ? colS1 : colS0) + 16 * cb2, cP = t_lane + (H ? colDP1 : colDP0) + 16 * cb2;
     const float scale = a.scale;
     const float inv_r = 1.f / (float)a.R;
     const float kInf = __int_as_float(0x7f800000);
@@ -419,7 +448,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
     // 32-bit shared-window addresses: every access below stays a shared-memory instruction
     const uint32_t sStage_s = smem_u32(sStage), sDS_s = smem_u32(sDS);
     const uint32_t out_s = smem_u32(sOut) + warp * L::kOutWarp;  // this warp's private staging area
-    const uint32_t brow0 = smem_u32(sBias) + (H * HT + 32 * cb2) * kBRow + jrow * (kBias16 ? 2 : 4);
+    const uint32_t brow0 = smem_u32(sBias) + (H * HT + 16 * cb2) * kBRow + jrow * (kBias16 ? 2 : 4);
     const uint32_t drow = sDS_s + H * (L::kDS / 2) + jrow * 128;
 
     // The residue mask of (b, s, key) in two halves, so that the load can be issued a step before
@@ -518,9 +547,6 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       if (warp == 0) { TR(0, 0) } else if (warp == 8) { TR(3, 0) }
       // the statistics vectors of this step are read with ordinary loads: observe their arrival here
       mbar_wait(st_full + stg, (n / kStages) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
-      mbar_wait(sd_full + H, n & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
-      tc_fence_after();
-      if (warp == 0) { TR(0, 1) } else if (warp == 8) { TR(3, 1) }
       if (has_bias && g == 0) mbar_wait(b_full + H, (n / G) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
       // a row whose keys are all dropped has nl = +inf for every query (the mask row is shared by
       // all queries of the MSA row): the whole step is uniform, P = 1/N_res, dS = 0
@@ -528,12 +554,19 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       uint32_t dk[16];
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
+        // quarter sub of this half: queries 32*sub + 16*cb2 .. +16 are this warp's
+        if (kSub == 2 || sub == 0) {
+          mbar_wait(sd_full + (2 * H + (kSub == 2 ? sub : 0)), n & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
+          tc_fence_after();
+        }
+        if (warp == 0) { TR(0, 1 + 4 * sub) } else if (warp == 8) { TR(3, 1 + 4 * sub) }
         uint32_t sr[16], dr[16];
-        tmem_ld16(cS + 16 * sub, sr);
-        tmem_ld16(cP + 16 * sub, dr);
-        const uint32_t vnl = vec_s + (H * HT + 32 * cb2 + 16 * sub) * 4, vdl = vnl + BT * 4;
-        const uint32_t brow = brow0 + (16 * sub) * kBRow;
+        tmem_ld16(cS + QT * sub, sr);
+        tmem_ld16(cP + QT * sub, dr);
+        const uint32_t vnl = vec_s + (H * HT + QT * sub + 16 * cb2) * 4, vdl = vnl + BT * 4;
+        const uint32_t brow = brow0 + (QT * sub) * kBRow;
         tmem_wait_ld();
+        if (warp == 0) { TR(0, 2 + 4 * sub) } else if (warp == 8) { TR(3, 2 + 4 * sub) }
         uint32_t pk[8];
         if (!deadstep) {
 #pragma unroll
@@ -581,8 +614,18 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
         }
         // P^T and dS^T, two 16-bit values per column, over the columns this thread has just read:
         // the A operands of the dV and dK MMAs (16 queries = 8 packed columns each)
-        tmem_st8(cS + 16 * sub, pk);
-        tmem_st8(cP + 16 * sub, *reinterpret_cast<uint32_t(*)[8]>(&dk[sub * 8]));
+        tmem_st8(cS + QT * sub, pk);
+        tmem_st8(cP + QT * sub, *reinterpret_cast<uint32_t(*)[8]>(&dk[sub * 8]));
+        if (warp == 0) { TR(0, 4 + 4 * sub) } else if (warp == 8) { TR(3, 4 + 4 * sub) }
+        // P^T and dS^T of the quarter are in tensor memory: its dV / dK MMAs may go
+        if (sub == 0 && H == 0 && cur.it == 0 && n >= SPI) drain_dkdv(pb, ph, ps0 + g, pj0, g);  // before those MMAs overwrite it
+        if (kSub == 2 || sub == 1) {
+          tmem_wait_st();
+          if (warp == 0) { TR(0, 3 + 4 * sub) } else if (warp == 8) { TR(3, 3 + 4 * sub) }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(cdone + (2 * H + (kSub == 2 ? sub : 0)));
+        }
         if (flush_dbias && last_of_group) {
           // The group's last row: this thread's 16 d_bias values of the chunk (one key, 16 queries) go
           // through the warp's staging area ([16 queries][32 keys]) and are added to d_bias in global
@@ -596,24 +639,18 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
           fence_async_shared();
           __syncwarp();
           if (lane == 0) {
-            tma_reduce_add_4d_s(&tmDB, out_s, cur.j0 + q4 * 32, cur.it * BT + H * HT + 32 * cb2 + 16 * sub, cur.h, cur.b);
+            tma_reduce_add_4d_s(&tmDB, out_s, cur.j0 + q4 * 32, cur.it * BT + H * HT + QT * sub + 16 * cb2, cur.h, cur.b);
             tma_commit_group();
           }
         }
       }
-      // P^T and dS^T are in tensor memory: the dV / dK MMAs of this half may go
-      if (H == 0 && cur.it == 0 && n >= SPI) drain_dkdv(pb, ph, ps0 + g, pj0, g);  // before those MMAs overwrite it
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(cdone + H);
       if (warp == 0) { TR(0, 10) } else if (warp == 8) { TR(3, 10) }
       // dS^T -> shared memory, [key][query] rows of 128 bytes per half, 128-byte swizzle; the tile is
       // free once the dQ MMAs of the previous step have read it
       mbar_wait(ds_empty, (n & 1) ^ 1, abort_s, a.status, DEV_TIMEOUT_MMA);
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        sts_v4(drow + (((4 * cb2 + c) ^ (jrow & 7)) << 4), dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
+      for (int c = 0; c < 4; ++c)  // dk[8 * sub + 4 * c2 ..]: queries 32 * sub + 16 * cb2 + 8 * c2 .. of this half
+        sts_v4(drow + (((4 * (c >> 1) + 2 * cb2 + (c & 1)) ^ (jrow & 7)) << 4), dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
       fence_async_shared();
       __syncwarp();
       if (lane == 0) {

@@ -289,23 +289,13 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
     const int row = (warp & 3) * 32 + lane;
     const uint32_t t_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + w * C::tmemWg;
     const float scale = a.scale;
-    // Shared memory is addressed through its 32-bit window (ld.shared / mbarrier on .shared): the
-    // same accesses through generic pointers are tracked like global loads.
-    const uint32_t bars_s = smem_u32(bars);
-    auto bar_s = [&](uint64_t* p) { return bars_s + static_cast<uint32_t>(p - bars) * 8u; };
-    const uint32_t abort_s = smem_u32(const_cast<int*>(abort_flag));
-    const uint32_t scratch_s = smem_u32(const_cast<uint32_t*>(scratch));
-    const uint32_t bias_row_s = smem_u32(smem + C::offB) + row * 128;  // my row of a staged bias tile
-    const uint32_t swz = static_cast<uint32_t>(row & 7);
-    const uint32_t mask_s = smem_u32(sMask), dirty_s = smem_u32(sDirty);
+    const F2 scale2 = f2_make(scale, scale);
     uint32_t g = 0, n_item = 0;  // running key-tile and item index
-#ifndef EVO_FWD_NOTURN
     // The two warpgroups take turns in the exponential phase (named barriers 1 and 2 pass a
     // token back and forth): while one keeps the MUFU busy, the other runs its load / bias /
     // mask / max phase on the FMA, ALU and shared-memory pipes instead of both queueing on
     // the same unit.
     if (w == 1) named_bar_arrive(1, 256);
-#endif
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
       const Item it = decode_item(item, NSP, NQT, a.H);
@@ -316,9 +306,9 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
 
       // residue-mask row of (b, s), staged by warp 3
       const uint32_t mst = n_item & 1;
-      mbar_wait_s(bar_s(m_full(w, mst)), (n_item >> 1) & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
-      const uint32_t mrow_base_s = mask_s + (w * 2 + mst) * r_pad * 4;
-      const uint32_t dirty_row_s = dirty_s + (w * 2 + mst) * 32 * 4;
+      mbar_wait(m_full(w, mst), (n_item >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
+      const float* mrow_base = sMask + (w * 2 + mst) * r_pad;
+      const uint32_t* dirty_row = sDirty + (w * 2 + mst) * 32;
 
       float m_run = -FLT_MAX, l_run = 0.f, alpha_pending = 1.f;
       float acc[DP];
@@ -326,53 +316,54 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
       for (int d = 0; d < DP; ++d) acc[d] = 0.f;
 
       for (int t = 0; t < T_TILES; ++t, ++g) {
-        mbar_wait_s(bar_s(s_full(w, g & 1)), (g >> 1) & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
+        mbar_wait(s_full(w, g & 1), (g >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
         tc_fence_after();
-        if (has_bias) mbar_wait_s(bar_s(b_full(g % BST)), (g / BST) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
-        const uint32_t bstage_s = bias_row_s + (g % BST) * C::kBias;
-        const uint32_t mrow_s = mrow_base_s + t * BN * 4;
+        if (has_bias) mbar_wait(b_full(g % BST), (g / BST) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        const uint8_t* bstage = smem + C::offB + (g % BST) * C::kBias + row * 128;
+        const float* mrow = mrow_base + t * BN;
 
-        // scores of my row: x = scale*S + bias, then the mask; four separate max chains
+        // scores of my row: x = scale*S + bias, then the mask.  Written in groups of eight
+        // independent elements (loads, FMAs, mins, then eight separate max chains) so that the
+        // in-order issue never waits on the previous instruction's result.
         float x[BN];
-        float mx4[4];
+        float mx8[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) mx4[u] = -FLT_MAX;
-        {
-          uint32_t sr[BN];
-          tmem_ld32(t_base + (g & 1) * BN, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
-          tmem_ld32(t_base + (g & 1) * BN + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < BN; ++e) x[e] = __uint_as_float(sr[e]);
-        }
+        for (int u = 0; u < 4; ++u) mx8[u] = -FLT_MAX;
+        uint32_t sr[BN];
+        tmem_ld32(t_base + (g & 1) * BN, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+        tmem_ld32(t_base + (g & 1) * BN + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+        tmem_wait_ld();
         // A key tile of a boolean mask without a dropped key needs neither the mask values nor
         // the `min` (most tiles: masks are mostly trailing padding); the flag is warp-uniform.
         auto scores = [&](auto with_mask) {
           constexpr bool kMask = decltype(with_mask)::value;
 #pragma unroll
           for (int g8 = 0; g8 < BN / 8; ++g8) {
+            const int c = g8 >> 2, q4 = (g8 & 3) * 2;
             float bvv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (has_bias) {
               if constexpr (BIAS16) {
                 // eight 16-bit values of my row (rows of 128 bytes, 128-byte swizzle), widened here
-                const float4 w4 = lds_v4f(bstage_s + ((static_cast<uint32_t>(g8) ^ swz) << 4));
-                const T* hv = reinterpret_cast<const T*>(&w4);
+                const uint4 w = *reinterpret_cast<const uint4*>(bstage + ((g8 ^ (row & 7)) << 4));
+                const T* hv = reinterpret_cast<const T*>(&w);
 #pragma unroll
                 for (int u = 0; u < 8; ++u) bvv[u] = to_float<T>(hv[u]);
               } else {
-                const uint32_t c = g8 >> 2, q4 = (g8 & 3) * 2;
-                const float4 b0 = lds_v4f(bstage_s + c * (C::kBias / 2) + ((q4 ^ swz) << 4));
-                const float4 b1 = lds_v4f(bstage_s + c * (C::kBias / 2) + (((q4 + 1) ^ swz) << 4));
+                const float4 b0 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + ((q4 ^ (row & 7)) << 4));
+                const float4 b1 = *reinterpret_cast<const float4*>(bstage + c * (C::kBias / 2) + (((q4 + 1) ^ (row & 7)) << 4));
                 bvv[0] = b0.x; bvv[1] = b0.y; bvv[2] = b0.z; bvv[3] = b0.w;
                 bvv[4] = b1.x; bvv[5] = b1.y; bvv[6] = b1.z; bvv[7] = b1.w;
               }
             }
             float v[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = fmaf(x[g8 * 8 + u], scale, bvv[u]);
+            for (int u = 0; u < 8; u += 2) {  // x = scale*S + bias, two elements per instruction
+              const F2 t = f2_fma(f2_from_bits(sr[g8 * 8 + u], sr[g8 * 8 + u + 1]), scale2, f2_make(bvv[u], bvv[u + 1]));
+              f2_get(t, v[u], v[u + 1]);
+            }
             if constexpr (kMask) {
-              const float4 k0 = lds_v4f(mrow_s + g8 * 32);
-              const float4 k1 = lds_v4f(mrow_s + g8 * 32 + 16);
+              const float4 k0 = *reinterpret_cast<const float4*>(mrow + g8 * 8);
+              const float4 k1 = *reinterpret_cast<const float4*>(mrow + g8 * 8 + 4);
               const float mkv[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
 #pragma unroll
               for (int u = 0; u < 8; ++u) v[u] = (MASKMODE == MASK_MIN) ? fminf(v[u], mkv[u]) : (v[u] + mkv[u]);
@@ -381,47 +372,74 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
             for (int u = 0; u < 8; u += 2) {
               x[g8 * 8 + u] = v[u];
               x[g8 * 8 + u + 1] = v[u + 1];
-              mx4[u >> 1] = max3(mx4[u >> 1], v[u], v[u + 1]);
+              mx8[u >> 1] = max3(mx8[u >> 1], v[u], v[u + 1]);
             }
           }
         };
         // (only where it measured faster: at D = 64 and D <= 16 the second copy of the loop costs
         // more than the skipped instructions save)
         if constexpr (DP == 32 && MASKMODE == MASK_MIN) {
-          if (lds_u32(dirty_row_s + t * 4) != 0u) scores(std::true_type{});
+          if (dirty_row[t] != 0u) scores(std::true_type{});
           else scores(std::false_type{});
         } else {
           scores(std::true_type{});
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float mx = fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3]));
         if (has_bias) {
           // The stage is handed back only after the bias loads above have returned: the store needs
           // the row maximum, which needs every one of them (an mbarrier arrival by itself does not
           // wait for shared loads that are still queued).
-          sts_u32(scratch_s, __float_as_uint(mx));
+          *scratch = __float_as_uint(mx);
           __syncwarp();
-          if (lane == 0) mbar_arrive_s(bar_s(b_empty(g % BST)));  // one arrival per warp
+          if (lane == 0) mbar_arrive(b_empty(g % BST));  // one arrival per warp
         }
 
         const float m_new = fmaxf(m_run, mx);
         const float alpha = ex2((m_run - m_new) * kLog2e);
         float lsum = 0.f;
         uint32_t pk[BN / 2];
-#ifndef EVO_FWD_NOTURN
         named_bar_sync(1 + w, 256);  // my turn on the exponential unit
-#endif
         if (m_new != -FLT_MAX) {
           const float nm2 = -m_new * kLog2e;
-          float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+          const F2 l2e2 = f2_make(kLog2e, kLog2e), nm22 = f2_make(nm2, nm2);
+          F2 ls4[4];
 #pragma unroll
-          for (int e = 0; e < BN; e += 2) {
-            const float p0 = ex2(fmaf(x[e], kLog2e, nm2));
-            const float p1 = ex2(fmaf(x[e + 1], kLog2e, nm2));
-            ls4[(e >> 1) & 3] += p0;
-            ls4[(e >> 1) & 3] += p1;
-            pk[e >> 1] = Pack2<T>::pack(p0, p1);
+          for (int u = 0; u < 4; ++u) ls4[u] = f2_make(0.f, 0.f);
+          // Software pipeline over groups of eight keys: the FMAs of group g+1 and the sum / pack of
+          // group g-1 are placed around the eight ex2 of group g, so the results of the
+          // exponential unit are not needed until a group later.
+          float y[8], p[8], pp[8];
+#pragma unroll
+          for (int u = 0; u < 8; u += 2) f2_get(f2_fma(f2_make(x[u], x[u + 1]), l2e2, nm22), y[u], y[u + 1]);
+#pragma unroll
+          for (int g8 = 0; g8 < BN / 8; ++g8) {
+            float yn[8];
+            if (g8 + 1 < BN / 8) {
+#pragma unroll
+              for (int u = 0; u < 8; u += 2)
+                f2_get(f2_fma(f2_make(x[(g8 + 1) * 8 + u], x[(g8 + 1) * 8 + u + 1]), l2e2, nm22), yn[u], yn[u + 1]);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) p[u] = ex2(y[u]);
+            if (g8 > 0) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                ls4[u] = f2_add(ls4[u], f2_make(pp[2 * u], pp[2 * u + 1]));
+                pk[(g8 - 1) * 4 + u] = Pack2<T>::pack(pp[2 * u], pp[2 * u + 1]);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { pp[u] = p[u]; y[u] = yn[u]; }
           }
-          lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            ls4[u] = f2_add(ls4[u], f2_make(pp[2 * u], pp[2 * u + 1]));
+            pk[(BN / 8 - 1) * 4 + u] = Pack2<T>::pack(pp[2 * u], pp[2 * u + 1]);
+          }
+          float lsa[8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) f2_get(ls4[u], lsa[2 * u], lsa[2 * u + 1]);
+          lsum = ((lsa[0] + lsa[1]) + (lsa[2] + lsa[3])) + ((lsa[4] + lsa[5]) + (lsa[6] + lsa[7]));
         } else {
           // every key seen so far was dropped: the scores are all -FLT_MAX and the softmax is
           // uniform over the real keys (test.py:54-55 semantics)
@@ -433,39 +451,38 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
             pk[e / 2] = Pack2<T>::pack(p0, p1);
           }
         }
-#ifndef EVO_FWD_NOTURN
         named_bar_arrive(2 - w, 256);  // hand the turn to the other warpgroup
-#endif
         l_run = l_run * alpha + lsum;
         m_run = m_new;
 
-        // P_n -> TMEM, packed two 16-bit values per column, over the first half of the S_n
-        // columns this thread has just consumed (lane = row, column j = keys 2j, 2j+1): the
-        // A operand of P V comes straight from tensor memory.
-        tmem_st32(t_base + (g & 1) * BN, pk);
-
         // fold the previous tile's P V into the accumulator (its MMA ran while we did the exps)
         if (t > 0) {
-          mbar_wait_s(bar_s(o_full(w, (g - 1) & 1)), ((g - 1) >> 1) & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
+          mbar_wait(o_full(w, (g - 1) & 1), ((g - 1) >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
           tc_fence_after();
           uint32_t orr[DP];
           tmem_ld<(DP >= 32 ? 32 : 16)>(t_base + 2 * BN + ((g - 1) & 1) * DP, *reinterpret_cast<uint32_t(*)[DP >= 32 ? 32 : 16]>(&orr[0]));
           if constexpr (DP == 64)
             tmem_ld32(t_base + 2 * BN + ((g - 1) & 1) * DP + 32, *reinterpret_cast<uint32_t(*)[32]>(&orr[32]));
           tmem_wait_ld();
+          const F2 ap2 = f2_make(alpha_pending, alpha_pending);
 #pragma unroll
-          for (int d = 0; d < DP; ++d) acc[d] = fmaf(acc[d], alpha_pending, __uint_as_float(orr[d]));
+          for (int d = 0; d < DP; d += 2)
+            f2_get(f2_fma(f2_make(acc[d], acc[d + 1]), ap2, f2_from_bits(orr[d], orr[d + 1])), acc[d], acc[d + 1]);
         }
         alpha_pending = alpha;
 
+        // P_n -> TMEM, packed two 16-bit values per column, over the first half of the S_n
+        // columns this thread has just consumed (lane = row, column j = keys 2j, 2j+1): the
+        // A operand of P V comes straight from tensor memory.
+        tmem_st32(t_base + (g & 1) * BN, pk);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_s(bar_s(p_full(w)));
+        if (lane == 0) mbar_arrive(p_full(w));
       }
       // last tile's P V
       {
-        mbar_wait_s(bar_s(o_full(w, (g - 1) & 1)), ((g - 1) >> 1) & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
+        mbar_wait(o_full(w, (g - 1) & 1), ((g - 1) >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
         tc_fence_after();
         uint32_t orr[DP];
         tmem_ld<(DP >= 32 ? 32 : 16)>(t_base + 2 * BN + ((g - 1) & 1) * DP, *reinterpret_cast<uint32_t(*)[DP >= 32 ? 32 : 16]>(&orr[0]));
@@ -503,11 +520,9 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         a.lse[li] = (m_run == -FLT_MAX) ? -FLT_MAX : (m_run + logf(l_run));
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive_s(bar_s(m_empty(w, mst)));
+      if (lane == 0) mbar_arrive(m_empty(w, mst));
     }
-#ifndef EVO_FWD_NOTURN
     if (w == 0) named_bar_sync(1, 256);  // consume the last token so no arrival is left pending
-#endif
   }
 
   if (*abort_flag) {

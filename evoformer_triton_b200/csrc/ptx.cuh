@@ -571,6 +571,21 @@ __device__ __forceinline__ void mma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint
       ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(b_step), "r"(idesc), "r"(acc_first)
       : "memory");
 }
+// The same with two MMAs (A advancing 16 columns, B advancing `b_step` units).
+__device__ __forceinline__ void mma_ts_x2(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t b_step,
+                                          uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 d0, d1;\n\t.reg .b32 a1, l1;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "add.u32 l1, %2, %4;\n\t"
+      "add.u32 a1, %1, 16;\n\t"
+      "mov.b64 d0, {%2, %3};\n\tmov.b64 d1, {l1, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d0, %5, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], d1, %5, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(b_step), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
 // Two D[tmem] = A[smem] * B[smem] over two K slices (descriptors advance by `k_step` units), then a
 // commit to `bar` (and to `bar2` if non-zero).
 __device__ __forceinline__ void mma_ss_x2_commit(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t k_step,
