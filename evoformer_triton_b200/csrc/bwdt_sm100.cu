@@ -38,8 +38,9 @@ using namespace ptx;
 constexpr int BT = 128;   // tile edge (queries and keys)
 constexpr int HT = 64;    // queries per half of a step (one warp group)
 constexpr int QT = 32;    // queries per quarter of a step
-// S^T / dP^T buffers per half: 1 = one of 64 queries, 2 = one per quarter (measured slower: forty
-// smaller MMAs per step instead of thirty-two, and twice the hand-overs)
+// S^T / dP^T buffers per half: 1 = one of 64 queries shared by the half's eight warps; 2 = one of 32
+// queries per group of four warps (four groups that hand over to the tensor core independently;
+// measured 2 % slower on the 384-residue workloads: forty smaller MMAs per step instead of thirty-two)
 constexpr int kSub = 1;
 constexpr int G = 3;      // MSA rows per work item
 constexpr int kCW = 16;   // compute warps
@@ -84,15 +85,6 @@ __device__ __forceinline__ void mbar_arrive(Bar b) { mbar_arrive_s(b.a); }
 __device__ __forceinline__ void mbar_expect_tx(Bar b, uint32_t bytes) { mbar_expect_tx_s(b.a, bytes); }
 __device__ __forceinline__ void mma_commit_if(uint32_t leader, Bar b) { mma_commit_if_s(leader, b.a); }
 
-// Debug build (-DEVO_PROF): cycles spent at each wait site, summed per warp role of CTA 0.
-// Debug build (-DEVO_TRACE): timestamps of selected points of steps kTrace0 .. kTrace0+2 of CTA 0.
-#ifdef EVO_TRACE
-__device__ long long g_trace[3][4][32];
-constexpr int kTrace0 = 20;
-#define TR(role, id) if (blockIdx.x == 0 && lane == 0 && n >= kTrace0 && n < kTrace0 + 3) g_trace[n - kTrace0][role][id] = clock64();
-#else
-#define TR(role, id)
-#endif
 
 // delta[b,h,s,i] = <dO_i, O_i> (evoformer.py:299-326) and nl = -lse*log2e, one thread per row.
 // A row whose keys were all dropped carries lse = -FLT_MAX from the forward; its nl is +inf, which
@@ -238,7 +230,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
     for (int i = 0; i < G; ++i) { mbar_init(bars + 0 + i, 1); mbar_init(bars + 3 + i, 3); }  // kv_full; kv_empty: three MMA warps read K/V
     for (int i = 0; i < kStages; ++i) { mbar_init(bars + 32 + i, 1); mbar_init(bars + 40 + i, 2); }  // st_full, st_empty
     for (int i = 0; i < 2; ++i) {
-      for (int q = 0; q < 2; ++q) { mbar_init(bars + 48 + 2 * i + q, 2); mbar_init(bars + 52 + 2 * i + q, kCW / 2); }  // sd_full, cdone
+      for (int q = 0; q < 2; ++q) { mbar_init(bars + 48 + 2 * i + q, 2); mbar_init(bars + 52 + 2 * i + q, kCW / (2 * kSub)); }  // sd_full, cdone
       mbar_init(bars + 14 + i, 1); mbar_init(bars + 16 + i, kCW / 2);  // b_full, b_done
       mbar_init(bars + 19 + i, 1);                                     // dq_full
       mbar_init(bars + 23 + i, kCW / 2);                               // sdone
@@ -329,7 +321,8 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             mbar_wait(cdone + (2 * h + sub), n & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
-            if (isA) { TR(1, 6 * sub + 3 * h) }
+            // (an item's first MMA of row g overwrites an accumulator that all warps of half 0 drain first)
+            if (kSub == 2 && h == 0 && sub == 0 && cur.it == 0) mbar_wait(cdone + 1, n & 1, abort_s, a.status, DEV_TIMEOUT_SYNC);
             tc_fence_after();
             const uint32_t tA = tmem + (h ? col_in1 : col_in0) + sub * QB;
             const uint32_t ba = ob + (4 * h + (4 / kSub) * sub) * kRowBlk;
@@ -337,7 +330,6 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
             if constexpr (kSub == 1) mma_ts_x4(acc, tA, ba, kHiOp, kRowBlk, kIdescOut, first);
             else mma_ts_x2(acc, tA, ba, kHiOp, kRowBlk, kIdescOut, first);
             if (h == 1 && sub == kSub - 1) mma_commit_if_s(1u, st_empty_bar);
-            if (isA) { TR(1, 6 * sub + 3 * h + 1) }
             if (more) {
               if (h == 0 && sub == 0) {
                 mbar_wait_s(st_full_bar, nxt.ring_par, abort_s, a.status, DEV_TIMEOUT_TMA);
@@ -346,7 +338,6 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
               }
               issue_in(nxt, ka, qb, h, sub);
             }
-            if (isA) { TR(1, 6 * sub + 3 * h + 2) }
           }
         }
         cur = nxt;
@@ -385,7 +376,6 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
             load_bias(nb, h);
           }
         }
-        TR(2, 0)
         tc_fence_after();
         const uint32_t ka = (kv_lo + (2 * g) * (L::kTile >> 4)) | kLoLbo;
         // dQ_i partial = dS K_j : A = dS^T tile [key][query] read MN-major (M = query), K runs over the keys
@@ -393,7 +383,6 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
         mma_commit_if(1u, dq_full + (n & 1));
         mma_commit_if(1u, ds_empty);
         if (it == NT - 1) mma_commit_if(1u, kv_empty + g);
-        TR(2, 2)
         if (++g == G) { g = 0; ++t; if (++it == NT) it = 0; }
       }
       }  // lane 0
@@ -440,7 +429,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
     const int q4 = warp & 3, cb2 = (warp >> 2) & 1, H = warp >> 3;
     const int jrow = q4 * 32 + lane;
     const uint32_t t_lane = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
-    const uint32_t cS = t_lane + (H ? colS1 : colS0) + 16 * cb2, cP = t_lane + (H ? colDP1 : colDP0) + 16 * cb2;
+    const uint32_t cS = t_lane + (H ? colS1 : colS0) + QT * cb2, cP = t_lane + (H ? colDP1 : colDP0) + QT * cb2;
     const float scale = a.scale;
     const float inv_r = 1.f / (float)a.R;
     const float kInf = __int_as_float(0x7f800000);
@@ -448,7 +437,7 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
     // 32-bit shared-window addresses: every access below stays a shared-memory instruction
     const uint32_t sStage_s = smem_u32(sStage), sDS_s = smem_u32(sDS);
     const uint32_t out_s = smem_u32(sOut) + warp * L::kOutWarp;  // this warp's private staging area
-    const uint32_t brow0 = smem_u32(sBias) + (H * HT + 16 * cb2) * kBRow + jrow * (kBias16 ? 2 : 4);
+    const uint32_t brow0 = smem_u32(sBias) + (H * HT + QT * cb2) * kBRow + jrow * (kBias16 ? 2 : 4);
     const uint32_t drow = sDS_s + H * (L::kDS / 2) + jrow * 128;
 
     // The residue mask of (b, s, key) in two halves, so that the load can be issued a step before
@@ -544,7 +533,6 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       const int stg = n % kStages;
       const uint32_t vec_s = sStage_s + stg * L::kStage + 2 * L::kTile;
       const bool last_of_group = (g == G - 1);
-      if (warp == 0) { TR(0, 0) } else if (warp == 8) { TR(3, 0) }
       // the statistics vectors of this step are read with ordinary loads: observe their arrival here
       mbar_wait(st_full + stg, (n / kStages) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
       if (has_bias && g == 0) mbar_wait(b_full + H, (n / G) & 1, abort_s, a.status, DEV_TIMEOUT_TMA);
@@ -554,19 +542,17 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       uint32_t dk[16];
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
-        // quarter sub of this half: queries 32*sub + 16*cb2 .. +16 are this warp's
-        if (kSub == 2 || sub == 0) {
-          mbar_wait(sd_full + (2 * H + (kSub == 2 ? sub : 0)), n & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
+        // this warp's queries of the half: 32*cb2 + 16*sub .. +16
+        if (sub == 0) {
+          mbar_wait(sd_full + (2 * H + (kSub == 2 ? cb2 : 0)), n & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
           tc_fence_after();
         }
-        if (warp == 0) { TR(0, 1 + 4 * sub) } else if (warp == 8) { TR(3, 1 + 4 * sub) }
         uint32_t sr[16], dr[16];
-        tmem_ld16(cS + QT * sub, sr);
-        tmem_ld16(cP + QT * sub, dr);
-        const uint32_t vnl = vec_s + (H * HT + QT * sub + 16 * cb2) * 4, vdl = vnl + BT * 4;
-        const uint32_t brow = brow0 + (QT * sub) * kBRow;
+        tmem_ld16(cS + 16 * sub, sr);
+        tmem_ld16(cP + 16 * sub, dr);
+        const uint32_t vnl = vec_s + (H * HT + QT * cb2 + 16 * sub) * 4, vdl = vnl + BT * 4;
+        const uint32_t brow = brow0 + (16 * sub) * kBRow;
         tmem_wait_ld();
-        if (warp == 0) { TR(0, 2 + 4 * sub) } else if (warp == 8) { TR(3, 2 + 4 * sub) }
         uint32_t pk[8];
         if (!deadstep) {
 #pragma unroll
@@ -614,17 +600,15 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
         }
         // P^T and dS^T, two 16-bit values per column, over the columns this thread has just read:
         // the A operands of the dV and dK MMAs (16 queries = 8 packed columns each)
-        tmem_st8(cS + QT * sub, pk);
-        tmem_st8(cP + QT * sub, *reinterpret_cast<uint32_t(*)[8]>(&dk[sub * 8]));
-        if (warp == 0) { TR(0, 4 + 4 * sub) } else if (warp == 8) { TR(3, 4 + 4 * sub) }
+        tmem_st8(cS + 16 * sub, pk);
+        tmem_st8(cP + 16 * sub, *reinterpret_cast<uint32_t(*)[8]>(&dk[sub * 8]));
         // P^T and dS^T of the quarter are in tensor memory: its dV / dK MMAs may go
-        if (sub == 0 && H == 0 && cur.it == 0 && n >= SPI) drain_dkdv(pb, ph, ps0 + g, pj0, g);  // before those MMAs overwrite it
-        if (kSub == 2 || sub == 1) {
+        if (sub == 1 && H == 0 && cur.it == 0 && n >= SPI) drain_dkdv(pb, ph, ps0 + g, pj0, g);  // before those MMAs overwrite it
+        if (sub == 1) {
           tmem_wait_st();
-          if (warp == 0) { TR(0, 3 + 4 * sub) } else if (warp == 8) { TR(3, 3 + 4 * sub) }
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(cdone + (2 * H + (kSub == 2 ? sub : 0)));
+          if (lane == 0) mbar_arrive(cdone + (2 * H + (kSub == 2 ? cb2 : 0)));
         }
         if (flush_dbias && last_of_group) {
           // The group's last row: this thread's 16 d_bias values of the chunk (one key, 16 queries) go
@@ -639,27 +623,24 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
           fence_async_shared();
           __syncwarp();
           if (lane == 0) {
-            tma_reduce_add_4d_s(&tmDB, out_s, cur.j0 + q4 * 32, cur.it * BT + H * HT + QT * sub + 16 * cb2, cur.h, cur.b);
+            tma_reduce_add_4d_s(&tmDB, out_s, cur.j0 + q4 * 32, cur.it * BT + H * HT + QT * cb2 + 16 * sub, cur.h, cur.b);
             tma_commit_group();
           }
         }
       }
-      if (warp == 0) { TR(0, 10) } else if (warp == 8) { TR(3, 10) }
       // dS^T -> shared memory, [key][query] rows of 128 bytes per half, 128-byte swizzle; the tile is
       // free once the dQ MMAs of the previous step have read it
       mbar_wait(ds_empty, (n & 1) ^ 1, abort_s, a.status, DEV_TIMEOUT_MMA);
 #pragma unroll
-      for (int c = 0; c < 4; ++c)  // dk[8 * sub + 4 * c2 ..]: queries 32 * sub + 16 * cb2 + 8 * c2 .. of this half
-        sts_v4(drow + (((4 * (c >> 1) + 2 * cb2 + (c & 1)) ^ (jrow & 7)) << 4), dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
+      for (int c = 0; c < 4; ++c)  // dk[4 * c ..]: queries 32 * cb2 + 8 * c .. of this half
+        sts_v4(drow + (((4 * cb2 + c) ^ (jrow & 7)) << 4), dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
       fence_async_shared();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(sdone + H);
         if (has_bias && last_of_group) mbar_arrive(b_done + H);
       }
-      if (warp == 0) { TR(0, 11) } else if (warp == 8) { TR(3, 11) }
       if (n > 0) send_dq(n - 1, prv);  // its MMAs ran underneath this step
-      if (warp == 0) { TR(0, 12) } else if (warp == 8) { TR(3, 12) }
       if (cur.it == NT - 1 && last_of_group) { pb = cur.b; ph = cur.h; ps0 = cur.s - g; pj0 = cur.j0; }
       prv = cur;
       cur = nxt;
@@ -749,9 +730,6 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
 
 }  // namespace
 
-#ifdef EVO_TRACE
-extern "C" int evoattn_debug_trace(void* dst, size_t bytes) { return (int)cudaMemcpyFromSymbol(dst, g_trace, bytes); }
-#endif
 
 size_t sm100_bwdt_workspace_bytes(const Args& a) {
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;

@@ -50,13 +50,11 @@ struct Cfg {
   static constexpr int BST = 2;                        // pair-bias stages (shared by both warpgroups)
   static constexpr int kQ = BM * RB;
   static constexpr int kKV = BN * RB;
-  static constexpr int kP = BM * BN * 2;               // 16 KB
   static constexpr int kBias = BM * BN * 4;            // 32 KB = two 128x32 fp32 boxes
   static constexpr int offQ = 0;
   static constexpr int offK = offQ + 2 * QST * kQ;
   static constexpr int offV = offK + 2 * NKV * kKV;
-  static constexpr int offP = offV + 2 * NKV * kKV;
-  static constexpr int offB = offP + 2 * kP;
+  static constexpr int offB = offV + 2 * NKV * kKV;
   static constexpr int offMask = offB + BST * kBias;
   static constexpr int kNumBars = 2 * (2 * QST + 4 * NKV + 2 + 1 + 2 + 4) + 2 * BST;
   static size_t bytes(int r_pad) {

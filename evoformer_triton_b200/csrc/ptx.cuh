@@ -77,7 +77,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 
 // The same primitives on 32-bit shared-window addresses (smem_u32 of the barrier, computed once):
 // no generic-pointer arithmetic or address-space conversion per call, and a wait loop that looks
-// at the clock and the abort flag only every 64th unsuccessful try.
+// at the clock and the abort flag only after every 1024 unsuccessful tries.
 __device__ __forceinline__ void mbar_arrive_s(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -106,19 +106,40 @@ __device__ __forceinline__ bool mbar_try_wait_parked_s(uint32_t bar, uint32_t pa
       : "memory");
   return ok != 0;
 }
+// Up to 1024 suspended tries in one tight loop (a waiting warp shares its scheduler with warps that
+// have arithmetic to issue: every instruction of the polling loop takes an issue slot from them).
+__device__ __forceinline__ bool mbar_try_wait_burst_s(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .u32 c;\n\t"
+      "mov.u32 c, 0;\n"
+      "EVO_W_AGAIN:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "@p bra EVO_W_DONE;\n\t"
+      "add.u32 c, c, 1;\n\t"
+      "setp.lt.u32 p, c, 1024;\n\t"
+      "@p bra EVO_W_AGAIN;\n\t"
+      "setp.ne.u32 p, 0, 0;\n"
+      "EVO_W_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(1000000u)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait_slow_s(uint32_t bar, uint32_t parity, uint32_t abort_flag_s, int* status, int code) {
-  const long long t0 = clock64();
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait_parked_s(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
-      uint32_t ab;
-      asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(ab) : "r"(abort_flag_s));
-      if (ab) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_flag_s), "r"(1u) : "memory");
-        if (status) atomicCAS(status, 0, code);
-        return false;
-      }
+  long long t0 = 0;
+  for (uint32_t round = 0;; ++round) {
+    if (mbar_try_wait_burst_s(bar, parity)) return true;
+    uint32_t ab;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(ab) : "r"(abort_flag_s));
+    if (ab) return false;
+    if (round == 0) {
+      t0 = clock64();
+    } else if (clock64() - t0 > kWaitLimitCycles) {
+      asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_flag_s), "r"(1u) : "memory");
+      if (status) atomicCAS(status, 0, code);
+      return false;
     }
   }
 }
