@@ -18,7 +18,7 @@ PATH_NONE, PATH_GENERIC, PATH_TCGEN05 = 0, 1, 2
 SYMBOLS = (
     "evoattn_abi_version", "evoattn_strerror", "evoattn_fwd", "evoattn_bwd_workspace_bytes",
     "evoattn_bwd", "evoattn_bwd_static_scratch", "evoattn_last_path", "evoattn_last_launch_count",
-    "evoattn_peer_flag_bytes", "evoattn_peer_buffer_create", "evoattn_peer_buffer_open",
+    "evoattn_peer_data_bytes", "evoattn_peer_flag_bytes", "evoattn_peer_buffer_create", "evoattn_peer_buffer_open",
     "evoattn_peer_buffer_close", "evoattn_peer_buffer_destroy", "evoattn_peer_allreduce_f32",
     "evoattn_bias_to_heads_first", "evoattn_dbias_to_heads_last",
 )
@@ -99,6 +99,8 @@ def load() -> C.CDLL:
         lib.evoattn_last_path.restype = C.c_int
         lib.evoattn_last_launch_count.restype = C.c_int
         lib.evoattn_peer_flag_bytes.restype = C.c_size_t
+        lib.evoattn_peer_data_bytes.restype = C.c_size_t
+        lib.evoattn_peer_data_bytes.argtypes = [C.c_uint64, C.c_int]
         lib.evoattn_peer_buffer_create.restype = C.c_int
         lib.evoattn_peer_buffer_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]
         lib.evoattn_peer_buffer_open.restype = C.c_int

@@ -5,12 +5,15 @@
 // dsevoformer-triton/evoformer.py:458 and the cast at :860); sharding the MSA rows over GPUs adds
 // one sum over ranks, and for the few megabytes involved a library all-reduce costs more in launch
 // and protocol latency than in bytes.  Here every rank maps every other rank's buffer (CUDA IPC)
-// and one kernel per rank does a two-shot all-reduce with plain peer loads and stores:
-//   barrier  - all ranks have finished writing their local sums
-//   rank r sums slice r over the ranks in a fixed order (so every rank ends with the same bits)
-//   and stores the result into slice r of every rank's buffer
+// and one kernel per rank does a two-shot all-reduce in which all traffic between GPUs is stores
+// (posted writes; a load from a peer costs a round trip of microseconds):
+//   rank r stores slice q of its local sums into rank q's staging area, for every q != r
+//   barrier  - all contributions to my slice have landed
+//   rank r adds up slice r over the ranks in rank order and stores the result into slice r of
+//   every rank's buffer
 //   barrier  - all slices have landed everywhere
-// Barriers are per thread block (block b of every rank meets block b of the others) through flag
+// The staging area follows the data in the same allocation (evoattn_peer_data_bytes).  Barriers
+// are per thread block (block b of every rank meets block b of the others) through flag
 // words in each rank's own memory that peers write with system-scope release stores; flags carry
 // an epoch that grows with every call, so they are never reset.  Every wait is bounded: when it
 // runs out the kernel records a code in the status word and goes on without waiting (the result
@@ -25,7 +28,7 @@ namespace evo {
 namespace {
 
 constexpr int kMaxPeers = 8;
-constexpr int kBlocks = 32;
+constexpr int kBlocks = 128;  // one per SM or fewer: blocks of different ranks wait for one another, all must be resident
 constexpr int kThreads = 512;
 constexpr long long kPeerWaitCycles = 4000000000LL;  // about two seconds
 
@@ -46,19 +49,25 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ float4 ld_peer_v4(const float4* p) {
-  float4 v;
-  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ float ld_peer_f32(const float* p) {
   float v;
   asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
   return v;
 }
 
+// Where the staging area starts inside a rank's allocation that holds `count` floats of data.
+__host__ __device__ inline unsigned long long stage_offset(unsigned long long count) { return (count * 4 + 255) / 256 * 256; }
+
+// Staged contributions were written by peers and published by the barrier's acquire.
+__device__ __forceinline__ float4 ld_staged_v4(const float4* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 __global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const PeerArgs p) {
   const int b = blockIdx.x, tid = threadIdx.x;
+  float tail_value = 0.f;
   // meet block b of every other rank: tell them, then wait for them (thread q handles rank q)
   auto barrier = [&](int which, int code) {
     __syncthreads();
@@ -78,37 +87,64 @@ __global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const PeerArgs
     __syncthreads();
   };
 
+  const unsigned long long n4 = p.count / 4;
+  const unsigned long long seg = (n4 + p.world - 1) / p.world;  // float4 per staging segment (one per contributing rank)
+  const unsigned long long stride = (unsigned long long)kBlocks * kThreads;
+  const unsigned long long t0 = (unsigned long long)b * kThreads + tid;
+  const float4* mine = reinterpret_cast<const float4*>(p.buf[p.rank]);
+  auto stage_of = [&](int q) { return reinterpret_cast<float4*>(reinterpret_cast<char*>(p.buf[q]) + stage_offset(p.count)); };
+
+  // my contribution to every other rank's slice goes into that rank's staging area, segment `rank`
+  for (int d = 1; d < p.world; ++d) {
+    const int q = (p.rank + d) % p.world;  // start with a different peer on every rank
+    const unsigned long long lo = n4 * q / p.world, hi = n4 * (q + 1) / p.world;
+    float4* dst = stage_of(q) + (unsigned long long)p.rank * seg;
+    for (unsigned long long i = lo + t0; i < hi; i += stride) dst[i - lo] = mine[i];
+  }
+
   barrier(0, DEV_TIMEOUT_SYNC);
 
-  const unsigned long long n4 = p.count / 4;
-  const unsigned long long lo = n4 * p.rank / p.world, hi = n4 * (p.rank + 1) / p.world;
-  for (unsigned long long i = lo + (unsigned long long)b * kThreads + tid; i < hi; i += (unsigned long long)kBlocks * kThreads) {
-    float4 v[kMaxPeers];
+  {
+    const unsigned long long lo = n4 * p.rank / p.world, hi = n4 * (p.rank + 1) / p.world;
+    const float4* stage = stage_of(p.rank);
+    for (unsigned long long i = lo + t0; i < hi; i += stride) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int q = 0; q < kMaxPeers; ++q)
-      if (q < p.world) v[q] = ld_peer_v4(reinterpret_cast<const float4*>(p.buf[q]) + i);
-    float4 acc = v[0];
+      for (int q = 0; q < kMaxPeers; ++q)  // rank order: the same bits whatever the timing
+        if (q < p.world) {
+          const float4 v = (q == p.rank) ? mine[i] : ld_staged_v4(stage + (unsigned long long)q * seg + (i - lo));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
 #pragma unroll
-    for (int q = 1; q < kMaxPeers; ++q)
-      if (q < p.world) { acc.x += v[q].x; acc.y += v[q].y; acc.z += v[q].z; acc.w += v[q].w; }
-#pragma unroll
-    for (int q = 0; q < kMaxPeers; ++q)
-      if (q < p.world) reinterpret_cast<float4*>(p.buf[q])[i] = acc;
+      for (int q = 0; q < kMaxPeers; ++q)
+        if (q < p.world) reinterpret_cast<float4*>(p.buf[q])[i] = acc;
+    }
   }
-  if (p.rank == 0 && b == 0 && tid < (int)(p.count & 3)) {  // the last count % 4 elements
-    const unsigned long long i = n4 * 4 + tid;
-    float acc = 0.f;
-    for (int q = 0; q < p.world; ++q) acc += ld_peer_f32(p.buf[q] + i);
-    for (int q = 0; q < p.world; ++q) p.buf[q][i] = acc;
+  if (p.count & 3) {  // the last count % 4 elements: every rank sums them itself, from the peers' buffers
+    // (they lie outside every slice, so nothing overwrites them before the second barrier)
+    if (b == 0 && tid < (int)(p.count & 3)) {
+      const unsigned long long i = n4 * 4 + tid;
+      float acc = 0.f;
+      for (int q = 0; q < p.world; ++q) acc += ld_peer_f32(p.buf[q] + i);
+      tail_value = acc;
+    }
   }
 
   barrier(1, DEV_TIMEOUT_SYNC);
+  // (all ranks have read the tail elements of all buffers: now each may overwrite its own)
+  if ((p.count & 3) && b == 0 && tid < (int)(p.count & 3)) p.buf[p.rank][n4 * 4 + tid] = tail_value;
 }
 
 }  // namespace
 }  // namespace evo
 
 extern "C" {
+
+size_t evoattn_peer_data_bytes(uint64_t count, int world) {
+  if (world < 1) world = 1;
+  const unsigned long long n4 = count / 4, seg = (n4 + world - 1) / world;
+  return (size_t)(evo::stage_offset(count) + (unsigned long long)world * seg * 16);
+}
 
 size_t evoattn_peer_flag_bytes(void) { return (size_t)2 * evo::kBlocks * evo::kMaxPeers * sizeof(uint32_t); }
 
@@ -152,7 +188,7 @@ int evoattn_peer_allreduce_f32(const evoattn_peer_allreduce_params* p, void* cud
   memset(&a, 0, sizeof(a));
   for (int q = 0; q < p->world; ++q) {
     if (!p->bufs[q] || !p->flags[q]) return EVOATTN_ERR_NULL;
-    if (((uintptr_t)p->bufs[q]) & 15) return EVOATTN_ERR_ALIGN;
+    if (((uintptr_t)p->bufs[q]) & 255) return EVOATTN_ERR_ALIGN;
     a.buf[q] = p->bufs[q];
     a.flag[q] = p->flags[q];
   }

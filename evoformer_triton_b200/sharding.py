@@ -93,9 +93,10 @@ class PeerReducer:
     dsevoformer-triton/evoformer.py:458,860).  With the MSA rows sharded, the local partial sums
     are a few megabytes, for which a library all-reduce is mostly launch and protocol latency.
     Here every rank maps every other rank's buffer (CUDA IPC over NVLink) and
-    ``evoattn_peer_allreduce_f32`` sums in place with one kernel per rank: rank r adds up slice r
-    over the ranks in a fixed order and stores it into every rank's buffer, between two flag
-    barriers whose waits are bounded.  All ranks end with the same bits.
+    ``evoattn_peer_allreduce_f32`` sums in place with one kernel per rank: every rank stores its
+    part of slice q into rank q's staging area, rank r adds up slice r in rank order and stores it
+    into every rank's buffer; two flag barriers with bounded waits separate the phases.  Only
+    stores cross NVLink, and all ranks end with the same bits.
 
     Set up once per (group, size); the op's backward writes its local d(pair_bias) straight into
     ``buffer(numel)`` and calls ``allreduce_``.  Construction is collective over ``group``.
@@ -118,7 +119,7 @@ class PeerReducer:
         bufs, flags = [], []
         with torch.cuda.device(self.device):
             try:
-                data_ptr, data_h = self._create(self.numel * 4)
+                data_ptr, data_h = self._create(int(self.lib.evoattn_peer_data_bytes(C.c_uint64(self.numel), self.world)))
                 flag_ptr, flag_h = self._create(int(self.lib.evoattn_peer_flag_bytes()))
             except RuntimeError as e:
                 err, data_ptr, flag_ptr, data_h, flag_h = e, 0, 0, None, None

@@ -172,24 +172,29 @@ int evoattn_bwd_static_scratch(const evoattn_bwd_params* p, void* cuda_stream);
  * complete after the local atomics (evoformer.py:458) and the cast (:860).  When the MSA rows
  * are sharded over GPUs, every rank holds a partial fp32 d(pair_bias) and the sum over ranks is
  * the one exchange step of the path.  evoattn_peer_allreduce_f32 does it in place with one kernel
- * per rank over NVLink (plain peer loads and stores, flag barriers with bounded waits; no
+ * per rank over NVLink (plain stores into the peers' memory, flag barriers with bounded waits; no
  * multicast): all ranks call it with the same count and epoch, and afterwards every rank's
  * buffer holds the same bits.
  *
  * Set-up (once, outside the hot path; these are the only functions of the library that allocate):
- * each rank creates a buffer for the data and one of evoattn_peer_flag_bytes() for the flags,
- * sends the 64-byte handles to the other ranks (any transport), and opens theirs. */
+ * each rank creates a data buffer of evoattn_peer_data_bytes(count, world) bytes (the first
+ * count floats are the data, the rest is a staging area that peers write into) and a flag buffer
+ * of evoattn_peer_flag_bytes(), sends the 64-byte handles to the other ranks (any transport), and
+ * opens theirs. */
 typedef struct evoattn_peer_allreduce_params {
   int32_t world;            /* GPUs taking part, 1..8 */
   int32_t rank;             /* this GPU's index */
   float* const* bufs;       /* host array [world]: every rank's data buffer as seen from this rank
-                               (bufs[rank] is this rank's own); 16-byte aligned */
+                               (bufs[rank] is this rank's own); 256-byte aligned, each of at least
+                               evoattn_peer_data_bytes(count, world) bytes */
   uint32_t* const* flags;   /* host array [world]: every rank's flag buffer, zero when created */
   uint64_t count;           /* floats to sum */
   uint32_t epoch;           /* 1, 2, 3, ... : one more with every call on these buffers */
   int32_t* status;          /* optional device word, set when a bounded wait runs out */
 } evoattn_peer_allreduce_params;
 
+/* Bytes of a data buffer that can take part in sums of up to `count` floats over `world` ranks. */
+size_t evoattn_peer_data_bytes(uint64_t count, int world);
 size_t evoattn_peer_flag_bytes(void);
 /* cudaMalloc + clear + IPC handle of a buffer other ranks may open. */
 int evoattn_peer_buffer_create(size_t bytes, void** dev_ptr, unsigned char handle_out[64]);
