@@ -527,7 +527,11 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
 
 template <class T>
 int launch_d(const Args& a, void* ws, size_t ws_bytes, cudaStream_t st, int* launches) {
+#ifdef EVO_D64_T
+  if (a.D <= 64)
+#else
   if (a.D <= 32)  // the kernel with transposed score tiles (bwdt_sm100.cu)
+#endif
     return launch_sm100_bwdt(std::is_same<T, __nv_bfloat16>::value ? EVOATTN_BF16 : EVOATTN_FP16, a, ws, ws_bytes, st,
                              launches);
   return launch_t<T, 64>(a, ws, ws_bytes, st, launches);
@@ -543,6 +547,9 @@ bool sm100_bwd_supported(int dtype, const Args& a) {
 }
 
 size_t sm100_bwd_workspace_bytes(int, const Args& a) {
+#ifdef EVO_D64_T
+  if (a.D <= 64) return sm100_bwdt_workspace_bytes(a);
+#endif
   if (a.D <= 32) return sm100_bwdt_workspace_bytes(a);
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;
   const size_t wide_bytes = (a.bias && a.bias16) ? (size_t)a.B * a.H * a.R * a.R * sizeof(float) : 0;

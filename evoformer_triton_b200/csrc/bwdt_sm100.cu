@@ -42,7 +42,9 @@ constexpr int QT = 32;    // queries per quarter of a step
 // queries per group of four warps (four groups that hand over to the tensor core independently;
 // measured 2 % slower on the 384-residue workloads: forty smaller MMAs per step instead of thirty-two)
 constexpr int kSub = 1;
-constexpr int G = 3;      // MSA rows per work item
+// MSA rows per work item: each keeps a dK and a dV accumulator of DP columns in tensor memory for the
+// whole item, next to 256 columns of score buffers and two dQ partials
+template <int DP> struct RowsPerItem { static constexpr int G = (DP == 64) ? 1 : 3; };
 constexpr int kCW = 16;   // compute warps
 constexpr int kThreadsT = 640;  // 16 compute + 4 service warps, five warps per scheduler
 constexpr int kComputeRegs = 112, kServiceRegs = 32;  // after setmaxnreg; the launch-time pool must hold their sum
@@ -51,6 +53,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 template <int DP>
 struct SmemT {
+  static constexpr int G = RowsPerItem<DP>::G;
   static constexpr int RB = DP * 2;                          // bytes per staged row
   static constexpr int kTile = BT * RB;                      // one Q, dO, K or V tile
   static constexpr int kVec = BT * 4;                        // one vector of row statistics
@@ -64,8 +67,13 @@ struct SmemT {
   static constexpr int offBias = offDS + kDS;
   static constexpr int offOut = offBias + kBias;
   static constexpr int offBars = offOut + kCW * kOutWarp;
-  static constexpr size_t bytes = offBars + 512 + 1024;  // 64 barrier slots (see the kernel), and the alignment slack
-  static_assert(offDS % 1024 == 0 && kStage % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+  // 64 barrier slots (see the kernel) and the slack for aligning the tiles to 1024 bytes.  At DP = 64
+  // only 512 bytes of slack fit: the kernel checks what the base address needs and gives up with a
+  // status code if it is more (the dynamic shared memory of a kernel without static shared memory
+  // starts on a 1024-byte boundary on this architecture, so it needs none).
+  static constexpr int kSlack = (DP == 64) ? 512 : 1024;
+  static constexpr size_t bytes = offBars + 512 + kSlack;
+  static_assert(offDS % 1024 == 0 && kStage % 1024 == 0 && offStage % 1024 == 0, "swizzled tiles need 1024-byte alignment");
   static_assert(bytes <= 232448, "shared memory budget of one CTA");
 };
 
@@ -156,7 +164,8 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
   constexpr int RB = L::RB;
   constexpr uint32_t SWZ = swizzle_code_for_row_bytes(RB);
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-  static_assert(DP == 32, "instantiated for a padded head dimension of 32");
+  static_assert(DP == 32 || DP == 64, "padded head dimension");
+  constexpr int G = RowsPerItem<DP>::G;
   constexpr int kTmemCols = 512;
   // TMEM: two (S^T, dP^T) half-tile buffers, the per-row dV and dK accumulators, two dQ partials
   constexpr int colS0 = 0, colDP0 = HT, colS1 = 2 * HT, colDP1 = 3 * HT;
@@ -165,6 +174,10 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (static_cast<int>(smem - smem_raw) > L::kSlack) {  // the same for every thread of every CTA
+    if (threadIdx.x == 0 && a.status) atomicCAS(a.status, 0, DEV_TIMEOUT_SYNC);
+    return;
+  }
   uint8_t* sKV = smem + L::offKV;
   uint8_t* sStage = smem + L::offStage;
   uint8_t* sDS = smem + L::offDS;
@@ -291,8 +304,14 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
       // scheduler with four arithmetic warps, so every instruction between the wake-up and the MMA is
       // paid several times over, and it sits on the critical path of the half that waits for it.
       auto issue_in = [&](const Pos& p, uint32_t ka, uint32_t qb, int h, int sub) {
-        mma_ss_x2_commit(tmem + (h ? col_in1 : col_in0) + sub * QB, ka, qb + (h * HT + sub * QB) * (RB >> 4), kHiOp, 2, kIdescSD,
-                         (sd_full + (2 * h + sub)).a, (h == 1 && sub == kSub - 1 && p.it == NT - 1) ? (kv_empty + p.g).a : 0u);
+        // (the second commit: the item's last read of this warp's K or V tile of row g)
+        const uint32_t bar2 = (h == 1 && sub == kSub - 1 && p.it == NT - 1) ? (kv_empty + p.g).a : 0u;
+        const uint32_t tD = tmem + (h ? col_in1 : col_in0) + sub * QB, qa = qb + (h * HT + sub * QB) * (RB >> 4);
+        if constexpr (DP == 32) {  // two K slices of 16
+          mma_ss_x2_commit(tD, ka, qa, kHiOp, 2, kIdescSD, (sd_full + (2 * h + sub)).a, bar2);
+        } else {                   // four
+          mma_ss_x4_commit(tD, ka, qa, kHiOp, 2, kIdescSD, (sd_full + (2 * h + sub)).a, bar2);
+        }
       };
       Pos cur{0, 0, 0u, 0u, 0u};
       if (total_steps > 0) {
@@ -466,53 +485,59 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
     };
 
     // dK, dV of row-group slot g (MSA row s of (b,h), keys j0..): TMEM -> registers -> global.
-    // Done by the warps of half 0 (16 of the 32 columns each): they are the ones whose arrival
-    // lets the next item's first MMAs overwrite the slot.
+    // Done by the warps of half 0 (half of the DP columns each, 16 at a time): they are the ones
+    // whose arrival lets the next item's first MMAs overwrite the slot.
     auto drain_dkdv = [&](int b, int h, int s, int j0, int g) {
       const int j = j0 + jrow;
-      uint32_t kr[16], vr[16];
-      tmem_ld16(t_lane + colDK + g * DP + cb2 * 16, kr);
-      tmem_ld16(t_lane + colDV + g * DP + cb2 * 16, vr);
-      tmem_wait_ld();
-      if (j < a.R && s < a.S) {
-        T* kd = reinterpret_cast<T*>(a.dk) + off4(a.sdk, b, h, s, j) + cb2 * 16;
-        T* vd = reinterpret_cast<T*>(a.dv) + off4(a.sdv, b, h, s, j) + cb2 * 16;
 #pragma unroll
-        for (int d8 = 0; d8 < 2; ++d8) {
-          if (cb2 * 16 + d8 * 8 < a.D) {
-            uint4 pk, pv;
-            pk.x = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 0]) * scale, __uint_as_float(kr[d8 * 8 + 1]) * scale);
-            pk.y = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 2]) * scale, __uint_as_float(kr[d8 * 8 + 3]) * scale);
-            pk.z = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 4]) * scale, __uint_as_float(kr[d8 * 8 + 5]) * scale);
-            pk.w = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 6]) * scale, __uint_as_float(kr[d8 * 8 + 7]) * scale);
-            pv.x = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 0]), __uint_as_float(vr[d8 * 8 + 1]));
-            pv.y = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 2]), __uint_as_float(vr[d8 * 8 + 3]));
-            pv.z = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 4]), __uint_as_float(vr[d8 * 8 + 5]));
-            pv.w = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 6]), __uint_as_float(vr[d8 * 8 + 7]));
-            *reinterpret_cast<uint4*>(kd + d8 * 8) = pk;
-            *reinterpret_cast<uint4*>(vd + d8 * 8) = pv;
+      for (int part = 0; part < DP / 32; ++part) {
+        const int c0 = cb2 * (DP / 2) + part * 16;
+        uint32_t kr[16], vr[16];
+        tmem_ld16(t_lane + colDK + g * DP + c0, kr);
+        tmem_ld16(t_lane + colDV + g * DP + c0, vr);
+        tmem_wait_ld();
+        if (j < a.R && s < a.S) {
+          T* kd = reinterpret_cast<T*>(a.dk) + off4(a.sdk, b, h, s, j) + c0;
+          T* vd = reinterpret_cast<T*>(a.dv) + off4(a.sdv, b, h, s, j) + c0;
+#pragma unroll
+          for (int d8 = 0; d8 < 2; ++d8) {
+            if (c0 + d8 * 8 < a.D) {
+              uint4 pk, pv;
+              pk.x = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 0]) * scale, __uint_as_float(kr[d8 * 8 + 1]) * scale);
+              pk.y = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 2]) * scale, __uint_as_float(kr[d8 * 8 + 3]) * scale);
+              pk.z = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 4]) * scale, __uint_as_float(kr[d8 * 8 + 5]) * scale);
+              pk.w = Pack2<T>::pack(__uint_as_float(kr[d8 * 8 + 6]) * scale, __uint_as_float(kr[d8 * 8 + 7]) * scale);
+              pv.x = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 0]), __uint_as_float(vr[d8 * 8 + 1]));
+              pv.y = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 2]), __uint_as_float(vr[d8 * 8 + 3]));
+              pv.z = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 4]), __uint_as_float(vr[d8 * 8 + 5]));
+              pv.w = Pack2<T>::pack(__uint_as_float(vr[d8 * 8 + 6]), __uint_as_float(vr[d8 * 8 + 7]));
+              *reinterpret_cast<uint4*>(kd + d8 * 8) = pk;
+              *reinterpret_cast<uint4*>(vd + d8 * 8) = pv;
+            }
           }
         }
       }
     };
-    // The dQ partial of step m at position d (TMEM lanes = queries): this warp's 8 columns of its 32
-    // query rows go through its staging area ([32 rows][8 floats]) into the fp32 accumulator in global
+    // The dQ partial of step m at position d (TMEM lanes = queries): this warp's DP/4 columns of its 32
+    // query rows go through its staging area ([32 rows][DP/4 floats]) into the fp32 accumulator in global
     // memory, as one small bulk tensor reduction that the warp issues itself.  It happens after the
     // warp's arrival, underneath the tensor core's turnaround for its half.
-    const int colblk = 2 * H + cb2;  // the 8 dQ columns this warp drains
+    constexpr int QC = DP / 4;       // dQ columns per warp (8 or 16)
+    const int colblk = 2 * H + cb2;  // which of the four column blocks this warp drains
     auto send_dq = [&](int m, const StepT& d) {
       mbar_wait(dq_full + (m & 1), (m >> 1) & 1, abort_s, a.status, DEV_TIMEOUT_MMA);
       tc_fence_after();
-      uint32_t qr[8];
-      tmem_ld8(t_lane + colDQ + (m & 1) * DP + colblk * 8, qr);
+      uint32_t qr[QC];
+      tmem_ld<QC>(t_lane + colDQ + (m & 1) * DP + colblk * QC, qr);
       staging_free();
       tmem_wait_ld();
-      sts_v4(out_s + lane * 32, qr[0], qr[1], qr[2], qr[3]);
-      sts_v4(out_s + lane * 32 + 16, qr[4], qr[5], qr[6], qr[7]);
+#pragma unroll
+      for (int c = 0; c < QC / 4; ++c)
+        sts_v4(out_s + lane * (QC * 4) + 16 * c, qr[4 * c], qr[4 * c + 1], qr[4 * c + 2], qr[4 * c + 3]);
       fence_async_shared();
       __syncwarp();
-      if (lane == 0 && d.s < a.S && colblk * 8 < a.D) {
-        tma_reduce_add_3d_s(&tmDQ, out_s, colblk * 8, d.it * BT + q4 * 32, (d.b * a.H + d.h) * a.S + d.s);
+      if (lane == 0 && d.s < a.S && colblk * QC < a.D) {
+        tma_reduce_add_3d_s(&tmDQ, out_s, colblk * QC, d.it * BT + q4 * 32, (d.b * a.H + d.h) * a.S + d.s);
         tma_commit_group();
       }
     };
@@ -670,9 +695,9 @@ evo_bwdt_kernel(const Args a, const int n_items, const __grid_constant__ CUtenso
 
 size_t align_up(size_t x, size_t al) { return (x + al - 1) / al * al; }
 
-template <class T>
+template <class T, int DP>
 int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* launches) {
-  constexpr int DP = 32;
+  constexpr int G = RowsPerItem<DP>::G;
   using L = SmemT<DP>;
   Args a = a0;
   const size_t rows = (size_t)a.B * a.H * a.S * a.R;
@@ -688,7 +713,7 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (!make_qkv_map(&tk, a.k, a.sk, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tv, a.v, a.sv, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tdo, a.d_o, a.sdo, a.B, a.H, a.S, a.R, a.D, DP, BT)) return EVOATTN_ERR_CUDA;
-  if (!make_rows_f32_plain_map(&tdq, dq_acc, a.D, a.R, (long long)a.B * a.H * a.S, 8, 32)) return EVOATTN_ERR_CUDA;
+  if (!make_rows_f32_plain_map(&tdq, dq_acc, a.D, a.R, (long long)a.B * a.H * a.S, DP / 4, 32)) return EVOATTN_ERR_CUDA;
   if (!make_stats_map(&tnl, nl, a.B * a.H, a.S, a.R, BT)) return EVOATTN_ERR_CUDA;
   if (!make_stats_map(&tdl, a.delta, a.B * a.H, a.S, a.R, BT)) return EVOATTN_ERR_CUDA;
   tb = tq;
@@ -738,8 +763,12 @@ size_t sm100_bwdt_workspace_bytes(const Args& a) {
 
 int launch_sm100_bwdt(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
                       int* launches) {
-  if (dtype == EVOATTN_BF16) return launch_t<__nv_bfloat16>(a, workspace, workspace_bytes, st, launches);
-  return launch_t<__half>(a, workspace, workspace_bytes, st, launches);
+  if (a.D <= 32) {
+    if (dtype == EVOATTN_BF16) return launch_t<__nv_bfloat16, 32>(a, workspace, workspace_bytes, st, launches);
+    return launch_t<__half, 32>(a, workspace, workspace_bytes, st, launches);
+  }
+  if (dtype == EVOATTN_BF16) return launch_t<__nv_bfloat16, 64>(a, workspace, workspace_bytes, st, launches);
+  return launch_t<__half, 64>(a, workspace, workspace_bytes, st, launches);
 }
 
 }  // namespace evo

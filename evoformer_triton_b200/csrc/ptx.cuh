@@ -625,6 +625,28 @@ __device__ __forceinline__ void mma_ss_x2_commit(uint32_t d_tmem, uint32_t a_lo,
       ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(k_step), "r"(idesc), "r"(bar), "r"(bar2)
       : "memory");
 }
+// The same over four K slices.
+__device__ __forceinline__ void mma_ss_x4_commit(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t k_step,
+                                                 uint32_t idesc, uint32_t bar, uint32_t bar2) {
+  asm volatile(
+      "{\n\t.reg .pred f, t, c;\n\t.reg .b64 da, db;\n\t.reg .b32 x, y;\n\t"
+      "setp.ne.b32 f, 0, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "setp.ne.b32 c, %7, 0;\n\t"
+      "mov.u32 x, %1;\n\tmov.u32 y, %2;\n\t"
+      "mov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, f;\n\t"
+      "add.u32 x, x, %4;\n\tadd.u32 y, y, %4;\n\tmov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, t;\n\t"
+      "add.u32 x, x, %4;\n\tadd.u32 y, y, %4;\n\tmov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, t;\n\t"
+      "add.u32 x, x, %4;\n\tadd.u32 y, y, %4;\n\tmov.b64 da, {x, %3};\n\tmov.b64 db, {y, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, t;\n\t"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+      "@c tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(k_step), "r"(idesc), "r"(bar), "r"(bar2)
+      : "memory");
+}
 // Eight D[tmem] = A[smem] * B[smem] (the first overwrites), A and B descriptors advancing by
 // `a_step` / `b_step` units per MMA, different high words.
 __device__ __forceinline__ void mma_ss_x8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t a_step, uint32_t b_lo,
