@@ -14,7 +14,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libevoattn.so")
-SOURCES = ["api.cu", "generic_kernels.cu", "tmap.cu", "fwd_sm100.cu", "bwd_sm100.cu", "bwdt_sm100.cu", "peer_reduce.cu", "extras.cu"]
+SOURCES = ["api.cu", "generic_kernels.cu", "tmap.cu", "fwd_sm100.cu", "bwd_sm100.cu", "peer_reduce.cu", "extras.cu"]
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr",

@@ -21,11 +21,6 @@ size_t sm100_bwd_workspace_bytes(int dtype, const Args& a);
 int launch_sm100_bwd(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
                      int* launches);
 
-// The fused backward with transposed score tiles (bwdt_sm100.cu; head dimensions 17..32).
-size_t sm100_bwdt_workspace_bytes(const Args& a);
-int launch_sm100_bwdt(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
-                      int* launches);
-
 // Backward half of the gated output (extras.cu): writes delta, the effective dO (into `scratch`) and
 // dgate, and redirects `a` to the effective dO.
 size_t gate_backward_scratch_bytes(int dtype, const Args& a);
