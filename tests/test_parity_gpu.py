@@ -149,6 +149,9 @@ SHAPES = [
     (1, 4, 200, 2, 32, torch.bfloat16, "add32", True),     # additive masks at D=32 (sixteen-warp backward)
     (1, 5, 136, 2, 32, torch.float16, "addsame", True),
     (1, 7, 384, 3, 24, torch.bfloat16, "add32", False),    # D < 32 padded, no pair bias, ragged row group
+    (1, 5, 200, 2, 48, torch.bfloat16, "bool", True),      # 32 < D < 64: the D=64 instantiation, padded columns
+    (2, 3, 264, 2, 40, torch.float16, "addsame", True),
+    (1, 40, 300, 8, 64, torch.bfloat16, "bool", True),     # D=64 with several work items per persistent CTA
 ]
 
 
@@ -213,6 +216,19 @@ def test_full_size_runs_are_reproducible():
     x = make_inputs(WORKLOADS["C2"])
     ref, _ = run_op(x)
     for _ in range(5):
+        got, _ = run_op(x)
+        for name, u, v in zip(NAMES, got, ref):
+            if name in ("O", "dK", "dV"):
+                assert torch.equal(u, v), f"{name} changed between two identical runs"
+
+
+def test_head_dim_64_runs_are_reproducible():
+    """The same for the head-dimension-64 instantiation of the backward (one MSA row per work item,
+    the pair-bias tile replaced every step) on a slice of C5 that gives every CTA several items."""
+    from evoformer_triton_b200.workloads import WORKLOADS, make_inputs
+    x = make_inputs(WORKLOADS["C5"], rows=24)
+    ref, _ = run_op(x)
+    for _ in range(3):
         got, _ = run_op(x)
         for name, u, v in zip(NAMES, got, ref):
             if name in ("O", "dK", "dV"):
@@ -328,7 +344,7 @@ def test_padded_bias_rows_with_odd_n_res():
 
 @pytest.mark.parametrize("cfg", [
     (1, 5, 200, 2, 32, torch.bfloat16), (1, 4, 384, 2, 32, torch.float16), (2, 3, 256, 2, 64, torch.bfloat16),
-    (1, 6, 136, 4, 8, torch.float16), (1, 3, 100, 2, 32, torch.bfloat16)],
+    (1, 6, 136, 4, 8, torch.float16), (1, 3, 100, 2, 32, torch.bfloat16), (1, 9, 392, 2, 56, torch.bfloat16)],
     ids=lambda c: "B%dS%dR%dH%dD%d-%s" % (c[0], c[1], c[2], c[3], c[4], str(c[5]).split(".")[-1]))
 def test_pair_bias_in_the_storage_type(cfg):
     """The pair bias in the 16-bit type of q/k/v, as the reference's benchmark scripts pass it
