@@ -95,17 +95,6 @@ __device__ __forceinline__ bool mbar_try_wait_s(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_try_wait_parked_s(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(1000000u)
-      : "memory");
-  return ok != 0;
-}
 // Up to 1024 suspended tries in one tight loop (a waiting warp shares its scheduler with warps that
 // have arithmetic to issue: every instruction of the polling loop takes an issue slot from them).
 __device__ __forceinline__ bool mbar_try_wait_burst_s(uint32_t bar, uint32_t parity) {
@@ -161,37 +150,11 @@ __device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
-// Bring the box into L2 without touching shared memory: a later load of it pays L2 latency only.
-__device__ __forceinline__ void tma_prefetch_5d(const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4) {
-  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %2, %3, %4, %5}];"
-               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-               : "memory");
-}
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
                                             int c3) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-// Tiled reduction shared -> global: global[tile] += shared[tile] (type and tile from the map).
-__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2,
-                                                  int c3) {
-  asm volatile(
-      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-      ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-      ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 __device__ __forceinline__ void tma_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -260,10 +223,6 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn_major, bo
 // Swizzled K-major tiles: rows of `swizzle` bytes, 8-row atoms, SBO = 8 * swizzle (next 8 rows).
 // Swizzled MN-major tiles: SBO = next 8 K-rows, LBO = next `swizzle`-byte block along M/N.
 constexpr uint32_t SWZ_128B = 2, SWZ_64B = 4, SWZ_32B = 6;
-__device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swz) {
-  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
-         (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (static_cast<uint64_t>(swz) << 61);
-}
 // The same encoding without the start address, usable in constant expressions, and the
 // assembly of a descriptor from a precomputed low word ((address >> 4) | leading-offset field)
 // and high word.
@@ -327,13 +286,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       EVO_I4(r, 28), "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
-      ::EVO_I4(r, 0), EVO_I4(r, 4), EVO_I4(r, 8), EVO_I4(r, 12), "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
                ::EVO_I4(r, 0), EVO_I4(r, 4), "r"(taddr)
@@ -345,12 +297,6 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8])
 // A load whose value is needed much later must not be followed by a select on its result: the
 // select would wait for the load where it stands.  These write the destination only when `pred`
 // holds and leave `dflt` in it otherwise; the address is not touched when `pred` is false.
-__device__ __forceinline__ float ldg_f32_if(const float* p, bool pred, float dflt) {
-  float v = dflt;
-  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q ld.global.f32 %0, [%1];\n\t}"
-               : "+f"(v) : "l"(p), "r"((int)pred));
-  return v;
-}
 __device__ __forceinline__ uint32_t ldg_u32_if(const void* p, bool pred) {
   uint32_t v = 0u;
   asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q ld.global.u32 %0, [%1];\n\t}"
@@ -380,11 +326,6 @@ __device__ __forceinline__ float lds_f32(uint32_t saddr) {
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(saddr));
   return v;
 }
-__device__ __forceinline__ uint32_t lds_u32(uint32_t saddr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
-  return v;
-}
 __device__ __forceinline__ uint16_t lds_u16(uint32_t saddr) {
   uint16_t v;
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(saddr));
@@ -397,9 +338,6 @@ __device__ __forceinline__ float4 lds_v4f(uint32_t saddr) {
 }
 __device__ __forceinline__ void sts_f32(uint32_t saddr, float v) {
   asm volatile("st.shared.f32 [%0], %1;" ::"r"(saddr), "f"(v) : "memory");
-}
-__device__ __forceinline__ void sts_u32(uint32_t saddr, uint32_t v) {
-  asm volatile("st.shared.u32 [%0], %1;" ::"r"(saddr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void sts_v4(uint32_t saddr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
@@ -434,19 +372,9 @@ __device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v));
   return r;
 }
-__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) {
-  F2 r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
-  return r;
-}
 __device__ __forceinline__ F2 f2_add(F2 a, F2 b) {
   F2 r;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
-  return r;
-}
-__device__ __forceinline__ F2 f2_sub(F2 a, F2 b) {
-  F2 r;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
   return r;
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -469,65 +397,9 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-// ---------------------------------------------------------------- leader-predicated forms
-// The control warps run their loops with all 32 lanes converged, so that addresses and
-// descriptors stay in uniform registers, and predicate only the instruction that must be issued
-// by a single thread (`leader` is non-zero in exactly one lane).
-__device__ __forceinline__ void mma_ss_if(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "setp.ne.b32 q, %5, 0;\n\t"
-      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts_if(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "setp.ne.b32 q, %5, 0;\n\t"
-      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit_if(uint32_t leader, uint64_t* bar) {
-  asm volatile(
-      "{\n\t.reg .pred q;\n\t"
-      "setp.ne.b32 q, %1, 0;\n\t"
-      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
-      ::"r"(smem_u32(bar)), "r"(leader)
-      : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx_if(uint32_t leader, uint64_t* bar, uint32_t bytes) {
-  asm volatile(
-      "{\n\t.reg .pred q;\n\t"
-      "setp.ne.b32 q, %2, 0;\n\t"
-      "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
-      ::"r"(smem_u32(bar)), "r"(bytes), "r"(leader)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_5d_if(uint32_t leader, void* dst, const CUtensorMap* map, uint64_t* bar,
-                                               int c0, int c1, int c2, int c3, int c4) {
-  asm volatile(
-      "{\n\t.reg .pred q;\n\t"
-      "setp.ne.b32 q, %8, 0;\n\t"
-      "@q cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n\t}"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(leader)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_4d_if(uint32_t leader, void* dst, const CUtensorMap* map, uint64_t* bar,
-                                               int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "{\n\t.reg .pred q;\n\t"
-      "setp.ne.b32 q, %7, 0;\n\t"
-      "@q cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n\t}"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(leader)
-      : "memory");
-}
-
+// ---------------------------------------------------------------- leader-predicated commit
+// For a warp that runs with all 32 lanes converged and predicates only the instruction that must be
+// issued by a single thread (`leader` is non-zero in exactly one lane).
 __device__ __forceinline__ void mma_commit_if_s(uint32_t leader, uint32_t bar) {
   asm volatile(
       "{\n\t.reg .pred q;\n\t"
@@ -536,6 +408,7 @@ __device__ __forceinline__ void mma_commit_if_s(uint32_t leader, uint32_t bar) {
       ::"r"(bar), "r"(leader)
       : "memory");
 }
+// ---------------------------------------------------------------- TMA on 32-bit shared-window addresses
 __device__ __forceinline__ void tma_load_5d_s(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
                                               int c3, int c4) {
   asm volatile(
@@ -556,6 +429,7 @@ __device__ __forceinline__ void tma_load_3d_s(uint32_t dst, const CUtensorMap* m
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// Tiled reduction shared -> global: global[tile] += shared[tile] (type and tile from the map).
 __device__ __forceinline__ void tma_reduce_add_4d_s(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
   asm volatile(
       "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"

@@ -146,7 +146,7 @@ SHAPES = [
     (1, 1, 640, 1, 64, torch.bfloat16, "none", False),
     (1, 2, 96, 2, 24, torch.bfloat16, "bool", True),       # D not a power of two
     (1, 2, 50, 2, 32, torch.bfloat16, "bool", True),       # R % 4 != 0: CUDA-core path
-    (1, 4, 200, 2, 32, torch.bfloat16, "add32", True),     # additive masks at D=32 (sixteen-warp backward)
+    (1, 4, 200, 2, 32, torch.bfloat16, "add32", True),     # additive masks at D=32
     (1, 5, 136, 2, 32, torch.float16, "addsame", True),
     (1, 7, 384, 3, 24, torch.bfloat16, "add32", False),    # D < 32 padded, no pair bias, ragged row group
     (1, 5, 200, 2, 48, torch.bfloat16, "bool", True),      # 32 < D < 64: the D=64 instantiation, padded columns
