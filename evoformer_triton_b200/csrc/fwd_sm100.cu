@@ -16,6 +16,11 @@
 // score row t (= TMEM lane t) and all 64 columns of the current key tile, so the row
 // maximum and sum need no exchange between threads.
 //
+// With a single MSA row (N_seq = 1, the shape of the reference's own benchmark sweep) there is no
+// second row to pair: the kernel is then instantiated in query-pair mode, where an item is two
+// consecutive query tiles of the same row, the warpgroups share one K/V ring and each has its own
+// pair-bias tile in a stage.
+//
 // Per warpgroup and key tile n:  S_n = Q K_n^T lands in TMEM (double buffered); the
 // warpgroup turns it into P_n (rounded to the storage type as evoformer.py:84 does) and
 // writes it back over S_n in TMEM, from where it feeds the P V MMA as the A operand;
@@ -42,20 +47,22 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int MASK_MIN = 0;  // boolean keep-mask (or none): score = min(score, m), m = +-FLT_MAX
 constexpr int MASK_ADD = 1;  // additive mask
 
-template <int DP>
+template <int DP, bool QP>
 struct Cfg {
   static constexpr int RB = DP * 2;                    // bytes per staged row
   static constexpr int QST = (DP == 64) ? 1 : 2;       // Q stages per warpgroup
   static constexpr int NKV = (DP == 64) ? 2 : 4;       // K and V ring depth per warpgroup
   static constexpr int BST = 2;                        // pair-bias stages (shared by both warpgroups)
+  static constexpr int KVW = QP ? 1 : 2;               // K/V rings: one per warpgroup, or one shared (query-pair mode)
+  static constexpr int BTL = QP ? 2 : 1;               // pair-bias tiles per stage: one shared, or one per warpgroup
   static constexpr int kQ = BM * RB;
   static constexpr int kKV = BN * RB;
   static constexpr int kBias = BM * BN * 4;            // 32 KB = two 128x32 fp32 boxes
   static constexpr int offQ = 0;
   static constexpr int offK = offQ + 2 * QST * kQ;
-  static constexpr int offV = offK + 2 * NKV * kKV;
-  static constexpr int offB = offV + 2 * NKV * kKV;
-  static constexpr int offMask = offB + BST * kBias;
+  static constexpr int offV = offK + KVW * NKV * kKV;
+  static constexpr int offB = offV + KVW * NKV * kKV;
+  static constexpr int offMask = offB + BST * BTL * kBias;
   static constexpr int kNumBars = 2 * (2 * QST + 4 * NKV + 2 + 1 + 2 + 4) + 2 * BST;
   static size_t bytes(int r_pad) {
     return (size_t)offMask + (size_t)4 * r_pad * 4 + 4 * 32 * 4 + kNumBars * 8 + 64 + 1024;
@@ -64,24 +71,34 @@ struct Cfg {
   static constexpr int tmemWg = 2 * BN + 2 * DP;
 };
 
+// A work item: warpgroup w works on query tile qt[w] of MSA row s[w] of (b, h).  Row-pair mode: rows
+// 2p and 2p+1, the same query tile; query-pair mode: one row, query tiles 2p and 2p+1.
 struct Item {
-  int b, h, qt, sp;
+  int b, h, qt[2], s[2];
 };
-__device__ __forceinline__ Item decode_item(int idx, int NSP, int NQT, int H) {
+template <bool QP>
+__device__ __forceinline__ Item decode_item(int idx, int n_inner, int n_outer, int H) {
   Item it;
-  it.sp = idx % NSP; idx /= NSP;
-  it.qt = idx % NQT; idx /= NQT;
+  const int inner = idx % n_inner; idx /= n_inner;   // row pair (row-pair mode) or row (query-pair mode)
+  const int outer = idx % n_outer; idx /= n_outer;   // query tile, or pair of query tiles
   it.h = idx % H;
   it.b = idx / H;
+  if (QP) {
+    it.s[0] = it.s[1] = inner;
+    it.qt[0] = 2 * outer; it.qt[1] = 2 * outer + 1;
+  } else {
+    it.s[0] = 2 * inner; it.s[1] = 2 * inner + 1;
+    it.qt[0] = it.qt[1] = outer;
+  }
   return it;
 }
 
-template <class T, int DP, int MASKMODE, bool BIAS16>
+template <class T, int DP, int MASKMODE, bool BIAS16, bool QP>
 __global__ void __launch_bounds__(kThreads, 1)
 evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CUtensorMap tmQ,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmB) {
-  using C = Cfg<DP>;
+  using C = Cfg<DP, QP>;
   constexpr int RB = C::RB, QST = C::QST, NKV = C::NKV, BST = C::BST;
   constexpr uint32_t SWZ = swizzle_code_for_row_bytes(RB);
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
@@ -116,7 +133,9 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NQT = (a.R + BM - 1) / BM;
-  const int NSP = (a.S + 1) / 2;
+  // items: (b, h, outer, inner) with inner fastest
+  const int n_inner = QP ? a.S : (a.S + 1) / 2;
+  const int n_outer = QP ? (NQT + 1) / 2 : NQT;
   const bool has_bias = a.bias != nullptr;
 
   // A launch that follows a failed one returns at once (one reader, so the CTA agrees).
@@ -127,9 +146,9 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
   if (tid == 0) {
     for (int w = 0; w < 2; ++w) {
       for (int st = 0; st < QST; ++st) { mbar_init(q_full(w, st), 1); mbar_init(q_empty(w, st), 1); }
-      for (int st = 0; st < NKV; ++st) {
-        mbar_init(k_full(w, st), 1); mbar_init(k_empty(w, st), 1);
-        mbar_init(v_full(w, st), 1); mbar_init(v_empty(w, st), 1);
+      for (int st = 0; st < NKV; ++st) {  // (query-pair mode: both issuers release the one shared ring)
+        mbar_init(k_full(w, st), 1); mbar_init(k_empty(w, st), QP ? 2 : 1);
+        mbar_init(v_full(w, st), 1); mbar_init(v_empty(w, st), QP ? 2 : 1);
       }
       mbar_init(s_full(w, 0), 1); mbar_init(s_full(w, 1), 1);
       mbar_init(p_full(w), 4);  // one arrival per softmax warp
@@ -156,21 +175,21 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
       // =============================== TMA producer ===============================
       uint32_t qn[2] = {0, 0}, gt = 0;
       for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const Item it = decode_item(item, NSP, NQT, a.H);
+        const Item it = decode_item<QP>(item, n_inner, n_outer, a.H);
         int srow[2];
-        srow[0] = min(2 * it.sp, a.S - 1);
-        srow[1] = min(2 * it.sp + 1, a.S - 1);
-        for (int w = 0; w < 2; ++w) {
+        srow[0] = min(it.s[0], a.S - 1);
+        srow[1] = min(it.s[1], a.S - 1);
+        for (int w = 0; w < 2; ++w) {  // (a query tile beyond the last one loads as zeros)
           const int st = qn[w] % QST;
           mbar_wait(q_empty(w, st), ((qn[w] / QST) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
           mbar_expect_tx(q_full(w, st), C::kQ);
-          tma_load_5d(smem + C::offQ + (w * QST + st) * C::kQ, &tmQ, q_full(w, st), 0, it.qt * BM, srow[w], it.h, it.b);
+          tma_load_5d(smem + C::offQ + (w * QST + st) * C::kQ, &tmQ, q_full(w, st), 0, it.qt[w] * BM, srow[w], it.h, it.b);
           ++qn[w];
         }
         for (int t = 0; t < T_TILES; ++t, ++gt) {
           const int st = gt % NKV;
           const uint32_t par = ((gt / NKV) & 1) ^ 1;
-          for (int w = 0; w < 2; ++w) {
+          for (int w = 0; w < C::KVW; ++w) {
             mbar_wait(k_empty(w, st), par, abort_flag, a.status, DEV_TIMEOUT_SYNC);
             mbar_expect_tx(k_full(w, st), C::kKV);
             tma_load_5d(smem + C::offK + (w * NKV + st) * C::kKV, &tmK, k_full(w, st), 0, t * BN, srow[w], it.h, it.b);
@@ -178,17 +197,18 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
           if (has_bias) {
             const int bs = gt % BST;
             mbar_wait(b_empty(bs), ((gt / BST) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
-            uint8_t* dst = smem + C::offB + bs * C::kBias;
-            if constexpr (BIAS16) {  // one box of 128 rows x 64 16-bit values (rows of 128 bytes)
-              mbar_expect_tx(b_full(bs), C::kBias / 2);
-              tma_load_4d(dst, &tmB, b_full(bs), t * BN, it.qt * BM, it.h, it.b);
-            } else {                 // two boxes of 128 rows x 32 floats
-              mbar_expect_tx(b_full(bs), C::kBias);
-              tma_load_4d(dst, &tmB, b_full(bs), t * BN, it.qt * BM, it.h, it.b);
-              tma_load_4d(dst + C::kBias / 2, &tmB, b_full(bs), t * BN + 32, it.qt * BM, it.h, it.b);
+            mbar_expect_tx(b_full(bs), C::BTL * (BIAS16 ? C::kBias / 2 : C::kBias));
+            for (int u = 0; u < C::BTL; ++u) {  // one tile for both warpgroups, or one each
+              uint8_t* dst = smem + C::offB + (bs * C::BTL + u) * C::kBias;
+              if constexpr (BIAS16) {  // one box of 128 rows x 64 16-bit values (rows of 128 bytes)
+                tma_load_4d(dst, &tmB, b_full(bs), t * BN, it.qt[u] * BM, it.h, it.b);
+              } else {                 // two boxes of 128 rows x 32 floats
+                tma_load_4d(dst, &tmB, b_full(bs), t * BN, it.qt[u] * BM, it.h, it.b);
+                tma_load_4d(dst + C::kBias / 2, &tmB, b_full(bs), t * BN + 32, it.qt[u] * BM, it.h, it.b);
+              }
             }
           }
-          for (int w = 0; w < 2; ++w) {
+          for (int w = 0; w < C::KVW; ++w) {
             mbar_wait(v_empty(w, st), par, abort_flag, a.status, DEV_TIMEOUT_SYNC);
             mbar_expect_tx(v_full(w, st), C::kKV);
             tma_load_5d(smem + C::offV + (w * NKV + st) * C::kKV, &tmV, v_full(w, st), 0, t * BN, srow[w], it.h, it.b);
@@ -205,13 +225,14 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
       constexpr uint32_t kHiOp = static_cast<uint32_t>(make_sdesc_const(16, 8 * RB, SWZ) >> 32);
       constexpr uint32_t kLoLbo = static_cast<uint32_t>(make_sdesc_const(16, 0, 0) & 0xffffffffu);
       const uint32_t q_lo0 = (smem_u32(smem + C::offQ + w * QST * C::kQ) >> 4) | kLoLbo;
-      const uint32_t k_lo0 = (smem_u32(smem + C::offK + w * NKV * C::kKV) >> 4) | kLoLbo;
-      const uint32_t v_lo0 = (smem_u32(smem + C::offV + w * NKV * C::kKV) >> 4) | kLoLbo;
+      const int kw = QP ? 0 : w;  // the K/V ring this warpgroup reads
+      const uint32_t k_lo0 = (smem_u32(smem + C::offK + kw * NKV * C::kKV) >> 4) | kLoLbo;
+      const uint32_t v_lo0 = (smem_u32(smem + C::offV + kw * NKV * C::kKV) >> 4) | kLoLbo;
       const uint32_t tS = tmem + w * C::tmemWg, tO = tS + 2 * BN;
       uint32_t qn = 0, base = 0;  // items done, key tiles done
       auto issue_s = [&](uint32_t g) {  // g: running key-tile index
         const int st = g % NKV;
-        mbar_wait(k_full(w, st), (g / NKV) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        mbar_wait(k_full(kw, st), (g / NKV) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
         tc_fence_after();
         const uint32_t qa = q_lo0 + (qn % QST) * (C::kQ >> 4);
         const uint32_t ka = k_lo0 + st * (C::kKV >> 4);
@@ -219,12 +240,12 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         for (int kk = 0; kk < DP / 16; ++kk)
           mma_ss(tS + (g & 1) * BN, pack_desc(qa + kk * 2, kHiOp), pack_desc(ka + kk * 2, kHiOp), kIdescS,
                  kk > 0 ? 1u : 0u);
-        mma_commit(k_empty(w, st));
+        mma_commit(k_empty(kw, st));
         mma_commit(s_full(w, g & 1));
       };
       auto issue_pv = [&](uint32_t g) {
         const int st = g % NKV;
-        mbar_wait(v_full(w, st), (g / NKV) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
+        mbar_wait(v_full(kw, st), (g / NKV) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
         mbar_wait(p_full(w), g & 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
         tc_fence_after();
         const uint32_t va = v_lo0 + st * (C::kKV >> 4);
@@ -232,7 +253,7 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         for (int kk = 0; kk < BN / 16; ++kk)  // 16 keys = 8 packed columns of P per step
           mma_ts(tO + (g & 1) * DP, tS + (g & 1) * BN + kk * 8, pack_desc(va + kk * RB, kHiOp), kIdescO,
                  kk > 0 ? 1u : 0u);
-        mma_commit(v_empty(w, st));
+        mma_commit(v_empty(kw, st));
         mma_commit(o_full(w, g & 1));
       };
       for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
@@ -252,10 +273,10 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
       // Keys beyond R are always excluded.
       uint32_t n = 0;
       for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n) {
-        const Item it = decode_item(item, NSP, NQT, a.H);
+        const Item it = decode_item<QP>(item, n_inner, n_outer, a.H);
         const int st = n & 1;
         for (int w = 0; w < 2; ++w) {
-          const int s = min(2 * it.sp + w, a.S - 1);
+          const int s = min(it.s[w], a.S - 1);
           mbar_wait(m_empty(w, st), ((n >> 1) & 1) ^ 1, abort_flag, a.status, DEV_TIMEOUT_SYNC);
           float* dst = sMask + (w * 2 + st) * r_pad;
           uint32_t* dirty = sDirty + (w * 2 + st) * 32;
@@ -296,11 +317,11 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
     if (w == 1) named_bar_arrive(1, 256);
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
-      const Item it = decode_item(item, NSP, NQT, a.H);
-      const int s_raw = 2 * it.sp + w;
-      const bool active = s_raw < a.S;
-      const int s = active ? s_raw : a.S - 1;
-      const int i = it.qt * BM + row;
+      const Item it = decode_item<QP>(item, n_inner, n_outer, a.H);
+      const int s_raw = it.s[w];
+      const bool active = s_raw < a.S && it.qt[w] < NQT;
+      const int s = s_raw < a.S ? s_raw : a.S - 1;
+      const int i = it.qt[w] * BM + row;
 
       // residue-mask row of (b, s), staged by warp 3
       const uint32_t mst = n_item & 1;
@@ -317,7 +338,7 @@ evo_fwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         mbar_wait(s_full(w, g & 1), (g >> 1) & 1, abort_flag, a.status, DEV_TIMEOUT_MMA);
         tc_fence_after();
         if (has_bias) mbar_wait(b_full(g % BST), (g / BST) & 1, abort_flag, a.status, DEV_TIMEOUT_TMA);
-        const uint8_t* bstage = smem + C::offB + (g % BST) * C::kBias + row * 128;
+        const uint8_t* bstage = smem + C::offB + ((g % BST) * C::BTL + (QP ? w : 0)) * C::kBias + row * 128;
         const float* mrow = mrow_base + t * BN;
 
         // scores of my row: x = scale*S + bias, then the mask.  Written in groups of eight
@@ -544,9 +565,9 @@ int num_sms_of_current_device() {
   return n;
 }
 
-template <class T, int DP>
+template <class T, int DP, bool QP>
 int launch_t(const Args& a, cudaStream_t st, int* launches) {
-  using C = Cfg<DP>;
+  using C = Cfg<DP, QP>;
   CUtensorMap tq, tk, tv, tb;
   if (!make_qkv_map(&tq, a.q, a.sq, a.B, a.H, a.S, a.R, a.D, DP, BM)) return EVOATTN_ERR_CUDA;
   if (!make_qkv_map(&tk, a.k, a.sk, a.B, a.H, a.S, a.R, a.D, DP, BN)) return EVOATTN_ERR_CUDA;
@@ -561,12 +582,14 @@ int launch_t(const Args& a, cudaStream_t st, int* launches) {
   const int g_num_sms = num_sms_of_current_device();
   if (g_num_sms <= 0) return EVOATTN_ERR_CUDA;
   const int T_TILES = (a.R + BN - 1) / BN;
+  const int NQT = (a.R + BM - 1) / BM;
   const size_t smem = C::bytes(T_TILES * BN);
-  const long long items = (long long)a.B * a.H * ((a.R + BM - 1) / BM) * ((a.S + 1) / 2);
+  const long long items = QP ? (long long)a.B * a.H * ((NQT + 1) / 2) * a.S
+                             : (long long)a.B * a.H * NQT * ((a.S + 1) / 2);
   const int grid = (int)(items < g_num_sms ? items : g_num_sms);
   const bool add = a.mask_kind == EVOATTN_MASK_ADD_F32 || a.mask_kind == EVOATTN_MASK_ADD_SAME;
-  auto kern = a.bias16 ? (add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD, true> : evo_fwd_sm100_kernel<T, DP, MASK_MIN, true>)
-                       : (add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD, false> : evo_fwd_sm100_kernel<T, DP, MASK_MIN, false>);
+  auto kern = a.bias16 ? (add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD, true, QP> : evo_fwd_sm100_kernel<T, DP, MASK_MIN, true, QP>)
+                       : (add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD, false, QP> : evo_fwd_sm100_kernel<T, DP, MASK_MIN, false, QP>);
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return EVOATTN_ERR_CUDA;
   kern<<<grid, kThreads, smem, st>>>(a, (int)items, tq, tk, tv, tb);
@@ -574,11 +597,20 @@ int launch_t(const Args& a, cudaStream_t st, int* launches) {
   return cudaGetLastError() == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
 }
 
+// A single MSA row with several query tiles runs in query-pair mode (both warpgroups get work);
+// everything else pairs MSA rows, which shares the larger tile (the pair bias) between them.
+template <class T, int DP>
+int launch_mode(const Args& a, cudaStream_t st, int* launches) {
+  const int r_pad = (a.R + BN - 1) / BN * BN;
+  if (a.S == 1 && a.R > BM && Cfg<DP, true>::bytes(r_pad) <= 232448) return launch_t<T, DP, true>(a, st, launches);
+  return launch_t<T, DP, false>(a, st, launches);
+}
+
 template <class T>
 int launch_d(const Args& a, cudaStream_t st, int* launches) {
-  if (a.D <= 16) return launch_t<T, 16>(a, st, launches);
-  if (a.D <= 32) return launch_t<T, 32>(a, st, launches);
-  return launch_t<T, 64>(a, st, launches);
+  if (a.D <= 16) return launch_mode<T, 16>(a, st, launches);
+  if (a.D <= 32) return launch_mode<T, 32>(a, st, launches);
+  return launch_mode<T, 64>(a, st, launches);
 }
 
 }  // namespace

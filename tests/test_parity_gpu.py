@@ -152,6 +152,9 @@ SHAPES = [
     (1, 5, 200, 2, 48, torch.bfloat16, "bool", True),      # 32 < D < 64: the D=64 instantiation, padded columns
     (2, 3, 264, 2, 40, torch.float16, "addsame", True),
     (1, 40, 300, 8, 64, torch.bfloat16, "bool", True),     # D=64 with several work items per persistent CTA
+    (2, 1, 300, 4, 32, torch.bfloat16, "bool", True),      # one MSA row: the forward pairs query tiles (3 tiles: odd)
+    (1, 1, 640, 2, 8, torch.float16, "add32", True),
+    (3, 1, 1024, 2, 64, torch.bfloat16, "bool", True),
 ]
 
 
@@ -344,7 +347,7 @@ def test_padded_bias_rows_with_odd_n_res():
 
 @pytest.mark.parametrize("cfg", [
     (1, 5, 200, 2, 32, torch.bfloat16), (1, 4, 384, 2, 32, torch.float16), (2, 3, 256, 2, 64, torch.bfloat16),
-    (1, 6, 136, 4, 8, torch.float16), (1, 3, 100, 2, 32, torch.bfloat16), (1, 9, 392, 2, 56, torch.bfloat16)],
+    (1, 6, 136, 4, 8, torch.float16), (1, 3, 100, 2, 32, torch.bfloat16), (1, 9, 392, 2, 56, torch.bfloat16), (4, 1, 264, 2, 64, torch.bfloat16)],
     ids=lambda c: "B%dS%dR%dH%dD%d-%s" % (c[0], c[1], c[2], c[3], c[4], str(c[5]).split(".")[-1]))
 def test_pair_bias_in_the_storage_type(cfg):
     """The pair bias in the 16-bit type of q/k/v, as the reference's benchmark scripts pass it
