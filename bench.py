@@ -184,6 +184,8 @@ def main():
                          "if peer mapping is unavailable) or an NCCL all-reduce")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every step's kernels from Python instead of replaying a CUDA graph of one step")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -255,6 +257,49 @@ def main():
     launches_per_step = attention.launches["fwd"] + attention.launches["bwd"]
     paths = dict(attention.last_path)
 
+    # ---- one step (forward, backward, exchange) captured in a CUDA graph: the host then issues one
+    # launch per step instead of a dozen from Python (about 0.24 ms of host time per step, which
+    # eight ranks sharing one host do not always have).  Any failure to capture falls back to
+    # launching from Python; all ranks take the same path.
+    graph = None
+    # (not with the NCCL exchange: a process whose CUDA graph holds NCCL's kernels did not exit)
+    if not args.no_graph and (world == 1 or reducer is not None):
+        ok = torch.ones(1, device=dev)
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    zero_grads()
+                    step()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize()
+            zero_grads()
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_):
+                step()
+            torch.cuda.synchronize()
+            g_.replay()
+            torch.cuda.synchronize()
+            evo.check_device_status()
+            graph = g_
+        except Exception as e:  # noqa: BLE001
+            ok.zero_()
+            print(f"[rank {rank}] CUDA graph capture of the step failed ({type(e).__name__}: {e}); launching from Python", file=sys.stderr)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            graph = None
+            torch.cuda.synchronize()
+            zero_grads()
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            zero_grads()
+            step()
+
     # ---- timed region: device-resident inputs, L2 flushed between steps
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -264,11 +309,10 @@ def main():
     torch.cuda.synchronize()
     pairs = []
     for _ in range(args.steps):
-        zero_grads()
         flush.zero_()
         e0, e1 = ev(), ev()
         e0.record()
-        step()
+        run_step()
         e1.record()
         pairs.append((e0, e1))
     torch.cuda.synchronize()
@@ -421,6 +465,8 @@ def main():
                        "global_rows": w.S * world,
                        "l2": "256 MB buffer written between timed steps",
                        "collective": collective,
+                       "launch": ("one CUDA graph replay per step (forward, backward and the exchange captured once)"
+                                  if graph is not None else "every kernel launched from Python"),
                        "paths": {k: {0: "none", 1: "cuda-core", 2: "tcgen05"}[v] for k, v in paths.items()}},
             "frac_of_bf16_peak": value / (peaks["tflops"] * world),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
@@ -428,6 +474,8 @@ def main():
             "op_peak_mem_bytes": op_peak_mem, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    graph = None  # the captured step goes before the process group does
+    torch.cuda.synchronize()
     if world > 1:
         dist.destroy_process_group()
 

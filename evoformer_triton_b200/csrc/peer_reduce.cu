@@ -68,16 +68,22 @@ __device__ __forceinline__ float4 ld_staged_v4(const float4* p) {
 __global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const PeerArgs p) {
   const int b = blockIdx.x, tid = threadIdx.x;
   float tail_value = 0.f;
+  // The epoch of this call: the caller's, or (epoch 0) one more than this block's own counter, which
+  // lives behind the flags in this rank's flag buffer.  Every rank makes the same calls, so block b
+  // of every rank counts alike; a launch replayed from a CUDA graph, whose arguments are frozen,
+  // still gets a new epoch each time.
+  uint32_t* const my_count = p.flag[p.rank] + 2 * kBlocks * kMaxPeers + b;
+  const uint32_t epoch = p.epoch ? p.epoch : *reinterpret_cast<volatile uint32_t*>(my_count) + 1u;
   // meet block b of every other rank: tell them, then wait for them (thread q handles rank q)
   auto barrier = [&](int which, int code) {
     __syncthreads();
     if (tid < p.world) {
       __threadfence_system();
-      st_release_sys(p.flag[tid] + (which * kBlocks + b) * kMaxPeers + p.rank, p.epoch);
+      st_release_sys(p.flag[tid] + (which * kBlocks + b) * kMaxPeers + p.rank, epoch);
       const uint32_t* mine = p.flag[p.rank] + (which * kBlocks + b) * kMaxPeers + tid;
       const long long t0 = clock64();
       // epochs only grow: a value at or beyond this call's epoch means that rank has arrived
-      while ((int32_t)(ld_acquire_sys(mine) - p.epoch) < 0) {
+      while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
         if (clock64() - t0 > kPeerWaitCycles) {
           if (p.status) atomicCAS(p.status, 0, code);
           break;
@@ -131,6 +137,7 @@ __global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const PeerArgs
   }
 
   barrier(1, DEV_TIMEOUT_SYNC);
+  if (p.epoch == 0 && tid == 0) *my_count = epoch;
   // (all ranks have read the tail elements of all buffers: now each may overwrite its own)
   if ((p.count & 3) && b == 0 && tid < (int)(p.count & 3)) p.buf[p.rank][n4 * 4 + tid] = tail_value;
 }
@@ -146,7 +153,9 @@ size_t evoattn_peer_data_bytes(uint64_t count, int world) {
   return (size_t)(evo::stage_offset(count) + (unsigned long long)world * seg * 16);
 }
 
-size_t evoattn_peer_flag_bytes(void) { return (size_t)2 * evo::kBlocks * evo::kMaxPeers * sizeof(uint32_t); }
+size_t evoattn_peer_flag_bytes(void) {
+  return ((size_t)2 * evo::kBlocks * evo::kMaxPeers + evo::kBlocks) * sizeof(uint32_t);  // flags, then the blocks' call counters
+}
 
 int evoattn_peer_buffer_create(size_t bytes, void** dev_ptr, unsigned char handle_out[64]) {
   if (!dev_ptr || !handle_out || bytes == 0) return EVOATTN_ERR_NULL;

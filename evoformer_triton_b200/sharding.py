@@ -112,7 +112,6 @@ class PeerReducer:
             raise RuntimeError("PeerReducer serves the (at most 8) GPUs of one node")
         self.device = torch.device(device)
         self.numel = int(numel)
-        self.epoch = 0
         self._own = []
         self._opened = []
         err = None
@@ -177,11 +176,10 @@ class PeerReducer:
         """In-place sum over the ranks of the first ``numel`` floats of every rank's buffer, on the
         current stream.  Collective: every rank calls it with the same ``numel``."""
         from . import _lib, attention
-        self.epoch += 1
         p = _lib.PeerAllReduceParams()
         p.world, p.rank = self.world, self.rank
         p.bufs, p.flags = self._bufs, self._flags
-        p.count, p.epoch = int(numel), self.epoch
+        p.count, p.epoch = int(numel), 0  # the library counts the calls itself: the launch may be replayed from a CUDA graph
         p.status = attention._status_word(self.device).data_ptr()
         stream = torch.cuda.current_stream(self.device).cuda_stream
         with torch.cuda.device(self.device):

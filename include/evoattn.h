@@ -189,7 +189,10 @@ typedef struct evoattn_peer_allreduce_params {
                                evoattn_peer_data_bytes(count, world) bytes */
   uint32_t* const* flags;   /* host array [world]: every rank's flag buffer, zero when created */
   uint64_t count;           /* floats to sum */
-  uint32_t epoch;           /* 1, 2, 3, ... : one more with every call on these buffers */
+  uint32_t epoch;           /* 0: the library counts the calls on these buffers itself (in the flag
+                               buffer; the form to use when the launch is replayed from a CUDA graph);
+                               otherwise 1, 2, 3, ... : one more with every call.  Use one form only
+                               on a given set of buffers */
   int32_t* status;          /* optional device word, set when a bounded wait runs out */
 } evoattn_peer_allreduce_params;
 
