@@ -382,6 +382,53 @@ def test_bias_without_gradient_skips_dbias():
     assert oc.rel_err(Q.grad, want[1]) < 4e-3
 
 
+def test_forward_and_backward_replayed_from_a_cuda_graph():
+    """The op captured once in a CUDA graph (forward, autograd backward) and replayed on new input
+    values gives what launching it from Python gives: nothing in the library synchronises,
+    allocates outside torch's allocator or keeps per-call state on the host."""
+    import evoformer_triton_b200 as evo
+    x = rand_inputs(1, 6, 264, 2, 32, torch.bfloat16, seed=23)
+    y = rand_inputs(1, 6, 264, 2, 32, torch.bfloat16, seed=24)
+    st = {n: x[n].to(DEV).clone() for n in ("Q", "K", "V", "res_mask", "pair_bias", "dO")}
+    for n in ("Q", "K", "V", "pair_bias"):
+        st[n].requires_grad_()
+
+    def step():
+        out = evo.EvoformerAttention.apply(st["Q"], st["K"], st["V"], st["res_mask"], st["pair_bias"])
+        out.backward(st["dO"])
+        return out
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            for n in ("Q", "K", "V", "pair_bias"):
+                st[n].grad = None
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    for n in ("Q", "K", "V", "pair_bias"):
+        st[n].grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = step()
+    for src in (y, x):  # new values in the captured tensors, then the first ones again
+        with torch.no_grad():
+            for n in st:
+                st[n].copy_(src[n].to(DEV))
+        graph.replay()
+        torch.cuda.synchronize()
+        evo.check_device_status()
+        got = tuple(t.detach().cpu() for t in (out, st["Q"].grad, st["K"].grad, st["V"].grad, st["pair_bias"].grad))
+        want, _ = run_op(src)
+        for name, u, v in zip(NAMES, got, want):
+            if name in ("O", "dK", "dV"):
+                assert torch.equal(u, v), name
+            else:
+                assert oc.rel_err(u, v) < 4e-3, name
+    del graph
+
+
 def test_full_size_properties_c5_rows():
     """At C5's full N_res/H/D (a slice of its MSA rows): size-independent properties.
     Rows of P sum to 1, so with V = const the output is that constant and dQ, dK, d_bias
