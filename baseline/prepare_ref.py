@@ -37,5 +37,6 @@ def prepare(src: str) -> bool:
 
 
 if __name__ == "__main__":
-    src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/dsevoformer-triton"
+    default = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference", "dsevoformer-triton")
+    src = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("EVOFORMER_REFERENCE_DIR", default)
     print("copied" if prepare(src) else f"reference not found at {src}")
