@@ -8,7 +8,7 @@ import threading
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libevoattn.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 BF16, FP16, FP32 = 0, 1, 2
 MASK_NONE, MASK_BOOL, MASK_ADD_F32, MASK_ADD_SAME = 0, 1, 2, 3
 FLAG_FORCE_GENERIC = 1
@@ -45,6 +45,15 @@ class FwdParams(C.Structure):
     ]
 
 
+class PeerAllReduceParams(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32),
+        ("bufs", C.POINTER(C.c_void_p)), ("flags", C.POINTER(C.c_void_p)),
+        ("count", C.c_uint64), ("epoch", C.c_uint32),
+        ("status", C.c_void_p),
+    ]
+
+
 class BwdParams(C.Structure):
     _fields_ = [
         ("fwd", FwdParams),
@@ -56,15 +65,7 @@ class BwdParams(C.Structure):
         ("dgate", C.c_void_p),
         ("dgate_stride", C.c_int64 * 4),
         ("dmask", C.c_void_p),
-    ]
-
-
-class PeerAllReduceParams(C.Structure):
-    _fields_ = [
-        ("world", C.c_int32), ("rank", C.c_int32),
-        ("bufs", C.POINTER(C.c_void_p)), ("flags", C.POINTER(C.c_void_p)),
-        ("count", C.c_uint64), ("epoch", C.c_uint32),
-        ("status", C.c_void_p),
+        ("exchange", C.POINTER(PeerAllReduceParams)),
     ]
 
 

@@ -141,12 +141,14 @@ def attention_forward(q, k, v, mask, bias, scale, gate=None):
 
 
 def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True, dbias_out=None, gate=None,
-                       want_dmask=False):
+                       want_dmask=False, exchange=None):
     """Raw backward on attention-view tensors.  Returns (dq, dk, dv, dbias fp32 or None), plus
     ``dgate`` when ``gate`` is given (``o`` and ``d_o`` are then the gated output and its
     gradient) and the fp32 ``[B,S,R]`` gradient of an additive mask when ``want_dmask``.
     ``want_dbias=False`` skips d(pair_bias) (its reductions are the backward's largest stream
-    of writes; speed_benchmark.py:68 builds the bias without ``requires_grad``)."""
+    of writes; speed_benchmark.py:68 builds the bias without ``requires_grad``).  ``exchange``
+    (a ``PeerAllReduceParams`` whose own buffer is ``dbias_out``) makes the call sum d(pair_bias)
+    over the node's GPUs itself, next to its last kernel."""
     lib = _lib.load()
     B, H, S, R, D = q.shape
     dq = torch.empty((B, H, S, R, D), dtype=q.dtype, device=q.device)
@@ -168,6 +170,10 @@ def attention_backward(q, k, v, o, lse, mask, bias, scale, d_o, want_dbias=True,
         p.dmask = dmask.data_ptr()
     p.d_o, p.dq, p.dk, p.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     p.dbias = None if dbias is None else dbias.data_ptr()
+    if exchange is not None:
+        if dbias is None or dbias_out is None:
+            raise ValueError("the in-call exchange sums d(pair_bias) in the caller's exchange buffer")
+        p.exchange = C.pointer(exchange)
     p.do_stride, p.dq_stride, p.dk_stride, p.dv_stride = _strides4(d_o), _strides4(dq), _strides4(dk), _strides4(dv)
     need = lib.evoattn_bwd_workspace_bytes(C.byref(p))
     ws = torch.empty(max(int(need), 1), dtype=torch.uint8, device=q.device)
@@ -293,15 +299,17 @@ class _EvoformerAttentionBase(torch.autograd.Function):
         want_dmask = mask is not None and mask.is_floating_point() and ctx.needs_input_grad[3]
         reducer = ctx.reduce_group[1] if (ctx.reduce_group is not None and want_dbias) else None
         dbias_out = reducer.buffer(bias.numel()) if reducer is not None else None
+        # (with a peer reducer the call sums d(pair_bias) over the ranks itself, next to its last kernel)
         res = attention_backward(q, k, v, o, lse, mask, bias, ctx.softmax_scale, d_o, want_dbias=want_dbias,
-                                 dbias_out=dbias_out, gate=g, want_dmask=want_dmask)
+                                 dbias_out=dbias_out, gate=g, want_dmask=want_dmask,
+                                 exchange=None if reducer is None else reducer.exchange_params(bias.numel()))
         dq, dk, dv, dbias = res[:4]
         dgate, dmask = (res[4], res[5]) if len(res) > 4 else (None, None)
         d_pair_bias = None
         if dbias is not None:
             dtype, shape = ctx.bias_meta
             if reducer is not None:  # N_seq is sharded: the other ranks' rows belong to the sum
-                reducer.allreduce_(bias.numel())
+                pass                 # (summed inside the backward call)
             elif ctx.reduce_group is not None:
                 import torch.distributed as dist
                 dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=ctx.reduce_group[0])

@@ -72,6 +72,13 @@ int validate_bwd(const evoattn_bwd_params* p) {
   if (rc) return rc;
   if (!p->d_o || !p->dq || !p->dk || !p->dv) return EVOATTN_ERR_NULL;
   if (p->fwd.gate && !p->dgate) return EVOATTN_ERR_NULL;
+  if (p->exchange) {  // the in-call sum of d(pair_bias) over the node's GPUs works on the caller's exchange buffer
+    const evoattn_peer_allreduce_params* x = p->exchange;
+    if (!p->fwd.bias || !p->dbias || !x->bufs) return EVOATTN_ERR_NULL;
+    if (x->world < 1 || x->world > 8 || x->rank < 0 || x->rank >= x->world) return EVOATTN_ERR_SHAPE;
+    if (x->bufs[x->rank] != p->dbias) return EVOATTN_ERR_SHAPE;
+    if (x->count != (uint64_t)p->fwd.B * p->fwd.H * p->fwd.R * p->fwd.R) return EVOATTN_ERR_SHAPE;
+  }
   return EVOATTN_OK;
 }
 
@@ -81,6 +88,7 @@ void fill_bwd_args(const evoattn_bwd_params* p, evo::Args* a) {
   a->dbias = p->fwd.bias ? p->dbias : nullptr;
   a->sdo = str4(p->do_stride); a->sdq = str4(p->dq_stride); a->sdk = str4(p->dk_stride); a->sdv = str4(p->dv_stride);
   a->dmask = p->dmask;
+  a->exchange = p->exchange;
 }
 
 size_t generic_bwd_workspace(const evo::Args& a) {
@@ -167,7 +175,13 @@ int run_bwd(const evoattn_bwd_params* p, evo::Args& a, bool fast, void* scratch,
     return evo::launch_sm100_bwd(p->fwd.dtype, a, scratch, path_bytes, st, &g_last_launches);
   }
   g_last_path = EVOATTN_PATH_GENERIC;
-  return evo::launch_generic_bwd(p->fwd.dtype, a, st, &g_last_launches) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+  if (evo::launch_generic_bwd(p->fwd.dtype, a, st, &g_last_launches) != cudaSuccess) return EVOATTN_ERR_CUDA;
+  if (p->exchange) {  // (the CUDA-core kernels have nothing to run the exchange next to)
+    const int rc = evo::launch_peer_allreduce(p->exchange, st);
+    if (rc) return rc;
+    g_last_launches += 1;
+  }
+  return EVOATTN_OK;
 }
 
 }  // namespace

@@ -749,8 +749,21 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::bytes) != cudaSuccess)
     return EVOATTN_ERR_CUDA;
   kern<<<(unsigned)ctas, kThreadsT, L::bytes, st>>>(a, (int)items, tq, tk, tv, tdo, tb, tdb, tdq, tnl, tdl);
+  // d(pair_bias) is complete: its sum over the GPUs of the node, if the caller asked for one, runs on
+  // a stream of its own next to the dQ store below; the caller's stream waits for it at the end
+  cudaStream_t side = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  if (a.exchange) {
+    if (!exchange_lane(&side, &fork, &join)) return EVOATTN_ERR_CUDA;
+    if (cudaEventRecord(fork, st) != cudaSuccess || cudaStreamWaitEvent(side, fork, 0) != cudaSuccess) return EVOATTN_ERR_CUDA;
+    const int rc = launch_peer_allreduce(reinterpret_cast<const evoattn_peer_allreduce_params*>(a.exchange), side);
+    if (cudaEventRecord(join, side) != cudaSuccess) return EVOATTN_ERR_CUDA;  // (join even after a failed launch)
+    if (rc) { cudaStreamWaitEvent(st, join, 0); return rc; }
+    *launches += 1;
+  }
   const long long n8 = (long long)rows * (a.D / 8);
   dq_store_kernel<T><<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(a, dq_acc);
+  if (a.exchange && cudaStreamWaitEvent(st, join, 0) != cudaSuccess) return EVOATTN_ERR_CUDA;
   *launches += 3;
   return cudaGetLastError() == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
 }

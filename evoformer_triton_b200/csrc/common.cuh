@@ -55,6 +55,7 @@ struct Args {
   const void* gate;
   Str4 sgate;
   int delta_ready;  // backward: delta has been written already (gated path), the kernels must not recompute it
+  const void* exchange;  // backward: evoattn_peer_allreduce_params of the d(pair_bias) exchange, or null
   float* dmask;     // backward (CUDA-core kernels only): gradient of an additive mask, [B,S,R] fp32
 };
 

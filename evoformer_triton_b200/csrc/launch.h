@@ -21,6 +21,11 @@ size_t sm100_bwd_workspace_bytes(int dtype, const Args& a);
 int launch_sm100_bwd(int dtype, const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
                      int* launches);
 
+// The exchange of d(pair_bias) between the GPUs of a node (peer_reduce.cu), and the side stream
+// with its fork / join events on which a backward call runs it next to its last kernel.
+int launch_peer_allreduce(const evoattn_peer_allreduce_params* p, cudaStream_t st);
+bool exchange_lane(cudaStream_t* side, cudaEvent_t* fork, cudaEvent_t* join);
+
 // Backward half of the gated output (extras.cu): writes delta, the effective dO (into `scratch`) and
 // dgate, and redirects `a` to the effective dO.
 size_t gate_backward_scratch_bytes(int dtype, const Args& a);

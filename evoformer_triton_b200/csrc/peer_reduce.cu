@@ -22,7 +22,10 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "common.cuh"
+#include "launch.h"
 
 namespace evo {
 namespace {
@@ -143,6 +146,45 @@ __global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const PeerArgs
 }
 
 }  // namespace
+
+int launch_peer_allreduce(const evoattn_peer_allreduce_params* p, cudaStream_t st) {
+  if (!p || !p->bufs || !p->flags) return EVOATTN_ERR_NULL;
+  if (p->world < 1 || p->world > kMaxPeers || p->rank < 0 || p->rank >= p->world) return EVOATTN_ERR_SHAPE;
+  if (p->count == 0) return EVOATTN_OK;
+  PeerArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int q = 0; q < p->world; ++q) {
+    if (!p->bufs[q] || !p->flags[q]) return EVOATTN_ERR_NULL;
+    if (((uintptr_t)p->bufs[q]) & 255) return EVOATTN_ERR_ALIGN;
+    a.buf[q] = p->bufs[q];
+    a.flag[q] = p->flags[q];
+  }
+  a.world = p->world; a.rank = p->rank; a.count = p->count; a.epoch = p->epoch; a.status = p->status;
+  peer_allreduce_kernel<<<kBlocks, kThreads, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+}
+
+// The stream and the two events with which a backward call runs its exchange next to its last
+// kernel: one set per device, made at the first call that asks for it (which therefore must not be
+// inside a stream capture) and kept until the process ends.
+bool exchange_lane(cudaStream_t* side, cudaEvent_t* fork, cudaEvent_t* join) {
+  struct Lane { cudaStream_t s; cudaEvent_t f, j; bool ok; };
+  static Lane lanes[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  Lane& l = lanes[dev];
+  if (!l.ok) {
+    if (cudaStreamCreateWithFlags(&l.s, cudaStreamNonBlocking) != cudaSuccess) return false;
+    if (cudaEventCreateWithFlags(&l.f, cudaEventDisableTiming) != cudaSuccess) return false;
+    if (cudaEventCreateWithFlags(&l.j, cudaEventDisableTiming) != cudaSuccess) return false;
+    l.ok = true;
+  }
+  *side = l.s; *fork = l.f; *join = l.j;
+  return true;
+}
+
 }  // namespace evo
 
 extern "C" {
@@ -190,20 +232,7 @@ int evoattn_peer_buffer_close(void* dev_ptr) {
 int evoattn_peer_buffer_destroy(void* dev_ptr) { return cudaFree(dev_ptr) == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA; }
 
 int evoattn_peer_allreduce_f32(const evoattn_peer_allreduce_params* p, void* cuda_stream) {
-  if (!p || !p->bufs || !p->flags) return EVOATTN_ERR_NULL;
-  if (p->world < 1 || p->world > evo::kMaxPeers || p->rank < 0 || p->rank >= p->world) return EVOATTN_ERR_SHAPE;
-  if (p->count == 0) return EVOATTN_OK;
-  evo::PeerArgs a;
-  memset(&a, 0, sizeof(a));
-  for (int q = 0; q < p->world; ++q) {
-    if (!p->bufs[q] || !p->flags[q]) return EVOATTN_ERR_NULL;
-    if (((uintptr_t)p->bufs[q]) & 255) return EVOATTN_ERR_ALIGN;
-    a.buf[q] = p->bufs[q];
-    a.flag[q] = p->flags[q];
-  }
-  a.world = p->world; a.rank = p->rank; a.count = p->count; a.epoch = p->epoch; a.status = p->status;
-  evo::peer_allreduce_kernel<<<evo::kBlocks, evo::kThreads, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(a);
-  return cudaGetLastError() == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;
+  return evo::launch_peer_allreduce(p, reinterpret_cast<cudaStream_t>(cuda_stream));
 }
 
 }  // extern "C"

@@ -114,6 +114,7 @@ class PeerReducer:
         self.numel = int(numel)
         self._own = []
         self._opened = []
+        self._params = {}
         err = None
         bufs, flags = [], []
         with torch.cuda.device(self.device):
@@ -171,6 +172,22 @@ class PeerReducer:
         if numel > self.numel:
             raise ValueError(f"PeerReducer was set up for {self.numel} elements, asked for {numel}")
         return self._tensor[:numel]
+
+    def exchange_params(self, numel: int):
+        """The parameters with which ``evoattn_bwd`` sums the first ``numel`` floats of the buffers
+        over the ranks as part of the call (the structure stays alive with this object)."""
+        from . import _lib, attention
+        if numel > self.numel:
+            raise ValueError(f"PeerReducer was set up for {self.numel} elements, asked for {numel}")
+        p = self._params.get(numel)
+        if p is None:
+            p = _lib.PeerAllReduceParams()
+            p.world, p.rank = self.world, self.rank
+            p.bufs, p.flags = self._bufs, self._flags
+            p.count, p.epoch = int(numel), 0
+            p.status = attention._status_word(self.device).data_ptr()
+            self._params[numel] = p
+        return p
 
     def allreduce_(self, numel: int) -> None:
         """In-place sum over the ranks of the first ``numel`` floats of every rank's buffer, on the

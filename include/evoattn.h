@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define EVOATTN_ABI_VERSION 2
+#define EVOATTN_ABI_VERSION 3
 
 /* status codes (0 = success). */
 enum {
@@ -98,6 +98,8 @@ typedef struct evoattn_fwd_params {
   int64_t gate_stride[4]; /* element strides of (b,h,s,r) */
 } evoattn_fwd_params;
 
+struct evoattn_peer_allreduce_params;  /* below: the exchange between the GPUs of a node */
+
 typedef struct evoattn_bwd_params {
   evoattn_fwd_params fwd; /* same q,k,v,o,lse,mask,bias as the forward call (o and lse are inputs) */
   const void* d_o;        /* dO, attention view */
@@ -121,6 +123,13 @@ typedef struct evoattn_bwd_params {
                              (sum of dS over heads and queries; DS4Sci returns a gradient for both
                              biases, the reference returns None, evoformer.py:862).  Requests with
                              dmask set are served by the CUDA-core kernels */
+  const struct evoattn_peer_allreduce_params* exchange;
+                          /* optional (null: none): sum d(pair_bias) over the GPUs that share the MSA
+                             rows as part of this call.  dbias must then be this rank's exchange buffer
+                             (exchange->bufs[exchange->rank]) and exchange->count = B*H*R*R.  The sum is
+                             launched as soon as d(pair_bias) is complete, on a stream of the library's
+                             own, next to the call's remaining kernel; the call's stream then waits
+                             for it, so everything the call returns is ordered on `cuda_stream` as usual */
 } evoattn_bwd_params;
 
 /* ABI version of the loaded library; compare with EVOATTN_ABI_VERSION. */
