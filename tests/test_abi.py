@@ -69,6 +69,20 @@ def test_bad_requests_are_rejected_without_a_gpu(built_library):
     b.fwd.mask_kind = 0
     assert lib.evoattn_bwd(C.byref(b), None) == 1      # null gradients
     assert lib.evoattn_bwd_workspace_bytes(C.byref(b)) == 0
+    # the in-call exchange of d(pair_bias) must work on the caller's own exchange buffer
+    b.d_o = b.dq = b.dk = b.dv = 256
+    x = _lib.PeerAllReduceParams()
+    x.world, x.rank, x.count = 2, 0, 1
+    bufs = (C.c_void_p * 2)(512, 768)
+    x.bufs = bufs
+    b.exchange = C.pointer(x)
+    assert lib.evoattn_bwd(C.byref(b), None) == 1      # an exchange without a bias and its gradient
+    b.fwd.bias = 1024
+    b.dbias = 4096
+    assert lib.evoattn_bwd(C.byref(b), None) == 2      # dbias is not this rank's exchange buffer
+    b.dbias = 512
+    x.count = 7
+    assert lib.evoattn_bwd(C.byref(b), None) == 2      # count is not B*H*R*R
     assert "null" in _lib.strerror(1)
     assert _lib.strerror(12345) == "unknown status"
 
