@@ -191,8 +191,8 @@ evo_bwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
   const Bar kv_empty{bars_s + 8 * 3};    // [G] ... and every MMA that reads them has completed
   const Bar st_full{bars_s + 8 * 32};     // [2] Q, dO and the statistics vectors of a step landed
   const Bar st_empty{bars_s + 8 * 40};    // [2] ... the step's last dV/dK MMAs have completed
-  const Bar sd_full{bars_s + 8 * 48};    // [2][2] S^T and dP^T of quarter (h, sub) of a step are in TMEM
-  const Bar cdone{bars_s + 8 * 52};      // [2][2] the warps of half h have P^T and dS^T of quarter sub in TMEM (for the dV/dK MMAs)
+  const Bar sd_full{bars_s + 8 * 48};    // [2][kSub] S^T and dP^T of score buffer (h, sub) of a step are in TMEM
+  const Bar cdone{bars_s + 8 * 52};      // [2][kSub] the warps of that buffer have its P^T and dS^T in TMEM (for the dV/dK MMAs)
   const Bar sdone{bars_s + 8 * 23};      // [2] ... and have stored their half of dS in shared memory (for the dQ MMAs)
   const Bar b_full{bars_s + 8 * 14};     // [2] half h (64 queries) of the pair-bias tile landed
   const Bar b_done{bars_s + 8 * 16};     // [2] ... has been read for the last time
@@ -629,7 +629,7 @@ evo_bwd_sm100_kernel(const Args a, const int n_items, const __grid_constant__ CU
         // the A operands of the dV and dK MMAs (16 queries = 8 packed columns each)
         tmem_st8(cS + 16 * sub, pk);
         tmem_st8(cP + 16 * sub, *reinterpret_cast<uint32_t(*)[8]>(&dk[sub * 8]));
-        // P^T and dS^T of the quarter are in tensor memory: its dV / dK MMAs may go
+        // P^T and dS^T of this warp's score buffer are in tensor memory: its dV / dK MMAs may go
         if (sub == 1 && H == 0 && cur.it == 0 && n >= SPI) drain_dkdv(pb, ph, ps0 + g, pj0, g);  // before those MMAs overwrite it
         if (sub == 1) {
           tmem_wait_st();
