@@ -743,11 +743,9 @@ int launch_t(const Args& a0, void* ws, size_t ws_bytes, cudaStream_t st, int* la
                       : (a.bias16 ? evo_bwd_sm100_kernel<T, DP, true, true> : evo_bwd_sm100_kernel<T, DP, true, false>);
   // setmaxnreg.inc waits until the scheduler's register pool (five warps at the launch-time count)
   // has what it asks for: never launch a build whose pool cannot hold the warps' requests.
-  cudaFuncAttributes fa;
-  if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return EVOATTN_ERR_CUDA;
-  if ((kThreadsT / 128) * fa.numRegs < 4 * kComputeRegs + kServiceRegs) return EVOATTN_ERR_UNSUPPORTED;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::bytes) != cudaSuccess)
-    return EVOATTN_ERR_CUDA;
+  int num_regs = 0;
+  if (!kernel_ready(reinterpret_cast<const void*>(kern), (int)L::bytes, &num_regs)) return EVOATTN_ERR_CUDA;
+  if ((kThreadsT / 128) * num_regs < 4 * kComputeRegs + kServiceRegs) return EVOATTN_ERR_UNSUPPORTED;
   kern<<<(unsigned)ctas, kThreadsT, L::bytes, st>>>(a, (int)items, tq, tk, tv, tdo, tb, tdb, tdq, tnl, tdl);
   // d(pair_bias) is complete: its sum over the GPUs of the node, if the caller asked for one, runs on
   // a stream of its own next to the dQ store below; the caller's stream waits for it at the end

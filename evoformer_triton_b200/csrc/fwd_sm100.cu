@@ -590,8 +590,7 @@ int launch_t(const Args& a, cudaStream_t st, int* launches) {
   const bool add = a.mask_kind == EVOATTN_MASK_ADD_F32 || a.mask_kind == EVOATTN_MASK_ADD_SAME;
   auto kern = a.bias16 ? (add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD, true, QP> : evo_fwd_sm100_kernel<T, DP, MASK_MIN, true, QP>)
                        : (add ? evo_fwd_sm100_kernel<T, DP, MASK_ADD, false, QP> : evo_fwd_sm100_kernel<T, DP, MASK_MIN, false, QP>);
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    return EVOATTN_ERR_CUDA;
+  if (!kernel_ready(reinterpret_cast<const void*>(kern), (int)smem, nullptr)) return EVOATTN_ERR_CUDA;
   kern<<<grid, kThreads, smem, st>>>(a, (int)items, tq, tk, tv, tb);
   *launches += 1;
   return cudaGetLastError() == cudaSuccess ? EVOATTN_OK : EVOATTN_ERR_CUDA;

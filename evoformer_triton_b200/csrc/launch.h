@@ -4,9 +4,40 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 
+#include <mutex>
+#include <unordered_map>
+#include <utility>
+
 #include "common.cuh"
 
 namespace evo {
+
+// Per (device, kernel) facts that cost a driver call each: the dynamic shared memory limit that has
+// been set for the kernel and its launch-time register count.  Looked up on every launch, asked of
+// the driver once (the limit again only when a launch needs more than any before it).
+struct KernelFacts {
+  int smem_limit = 0;
+  int num_regs = 0;
+};
+inline bool kernel_ready(const void* kern, int smem_bytes, int* num_regs) {
+  static std::mutex mu;
+  static std::unordered_map<const void*, KernelFacts> facts[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  KernelFacts& f = facts[dev][kern];
+  if (f.num_regs == 0) {
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return false;
+    f.num_regs = fa.numRegs;
+  }
+  if (smem_bytes > f.smem_limit) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return false;
+    f.smem_limit = smem_bytes;
+  }
+  if (num_regs) *num_regs = f.num_regs;
+  return true;
+}
 
 // CUDA-core kernels (generic_kernels.cu).  Backward needs a.delta = [B,H,S,R] fp32 scratch.
 cudaError_t launch_generic_fwd(int dtype, const Args& a, cudaStream_t st, int* launches);
